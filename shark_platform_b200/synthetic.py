@@ -1,0 +1,173 @@
+"""Seeded synthetic MoE layers in the reference's tensor formats.
+
+Real Mixtral / Grok checkpoints cannot be fetched, so benchmarks and tests use
+random layers with the shapes of the public model configs and the value
+distributions the benchmark definition gives.  One CPU generator per case,
+draws in a fixed order: activations, router weight, [router bias], then the
+gate, up and down expert planes.  Plane names and shapes are those of
+sharktank's BlockScaledLayout (types/layouts.py:194-299) and
+SuperBlockOffsetScaled_4_6_Layout (types/layouts.py:360-530).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+Q8_0 = "Q8_0"
+Q4_K = "Q4_K"
+DENSE = "DENSE"
+
+
+@dataclass
+class CaseSpec:
+    name: str
+    tokens: int
+    hidden: int
+    ffn: int
+    experts: int = 8
+    top_k: int = 2
+    kind: str = Q8_0
+    activation: str = "silu"
+    act_dtype: str = "bf16"  # "bf16": activations rounded to bf16; "f32": kept
+    out_norm: bool = False
+    router_bias: Optional[str] = None  # None | "zipf" | "normal"
+    norm_weight: str = "ones"  # "ones" | "perturbed"
+    seed: int = 0
+    eps: float = 1e-5
+
+
+# The five benchmark configurations plus reduced shapes used by fixtures.
+CASES = {
+    "toy": CaseSpec("toy", 64, 512, 1024, kind=DENSE, act_dtype="f32", seed=0),
+    "mixtral_q8": CaseSpec("mixtral_q8", 32, 4096, 14336, kind=Q8_0, seed=1),
+    "mixtral_q4k": CaseSpec("mixtral_q4k", 32, 4096, 14336, kind=Q4_K, seed=2),
+    "grok_q8": CaseSpec(
+        "grok_q8", 8192, 6144, 32768, kind=Q8_0, activation="gelu", out_norm=True, seed=3
+    ),
+    "small_q8": CaseSpec(
+        "small_q8", 40, 256, 512, kind=Q8_0, norm_weight="perturbed", seed=11
+    ),
+    "small_q4k": CaseSpec(
+        "small_q4k", 33, 256, 512, kind=Q4_K, norm_weight="perturbed", seed=12
+    ),
+    "small_grok": CaseSpec(
+        "small_grok", 17, 256, 768, kind=Q8_0, activation="gelu", out_norm=True,
+        router_bias="zipf", norm_weight="perturbed", seed=13,
+    ),
+    "small_top4": CaseSpec(
+        "small_top4", 29, 256, 512, kind=Q8_0, top_k=4, router_bias="normal",
+        norm_weight="perturbed", seed=14,
+    ),
+    "small_dense": CaseSpec(
+        "small_dense", 21, 256, 512, kind=DENSE, act_dtype="f32",
+        norm_weight="perturbed", seed=15,
+    ),
+}
+
+
+def zipf_bias(gen: torch.Generator, experts: int, s: float = 1.2) -> torch.Tensor:
+    """Per-expert router bias from a Zipf(s) ranking: a random permutation gives
+    expert e a rank r_e in 1..E and the bias is -s*ln(r_e) (prior odds r^-s)."""
+    rank = torch.randperm(experts, generator=gen) + 1
+    return (-s * torch.log(rank.to(torch.float32))).contiguous()
+
+
+def q8_0_planes(gen, experts: int, n: int, k: int) -> dict:
+    """int8 quants uniform in [-127,127], fp16 scales |N(0,1)|*0.002."""
+    qs = torch.randint(-127, 128, (experts, n, k // 32, 32), generator=gen, dtype=torch.int8)
+    d = (torch.randn(experts, n, k // 32, 1, generator=gen).abs() * 0.002).to(torch.float16)
+    return {"d": d, "qs": qs}
+
+
+def q4_k_planes(gen, experts: int, n: int, k: int) -> dict:
+    """Uniform 4-bit quants, uniform 6-bit sub-scales and sub-mins in the
+    planar hi/low planes; d = |N(0,1)|*2.5e-4 and dmin = |N(0,1)|*2e-3 keep the
+    weights zero-mean and comparable in size to the Q8_0 case."""
+    sup = k // 256
+    qs = torch.randint(0, 256, (experts, n, sup, 8, 16), generator=gen, dtype=torch.uint8)
+
+    def six_bit():
+        v = torch.randint(0, 64, (experts, n, sup, 8), generator=gen, dtype=torch.uint8)
+        lo, hi = v & 0xF, v >> 4
+        low = lo[..., 0::2] | (lo[..., 1::2] << 4)
+        high = hi[..., 0::4] | (hi[..., 1::4] << 2) | (hi[..., 2::4] << 4) | (hi[..., 3::4] << 6)
+        return high.contiguous(), low.contiguous()
+
+    sc_hi, sc_lo = six_bit()
+    mn_hi, mn_lo = six_bit()
+    d = (torch.randn(experts, n, sup, 1, generator=gen).abs() * 2.5e-4).to(torch.float16)
+    dmin = (torch.randn(experts, n, sup, 1, generator=gen).abs() * 2.0e-3).to(torch.float16)
+    return {
+        "d": d, "dmin": dmin,
+        "sb_scales_high": sc_hi, "sb_scales_low": sc_lo,
+        "sb_mins_high": mn_hi, "sb_mins_low": mn_lo,
+        "qs": qs,
+    }
+
+
+def dense_planes(gen, experts: int, n: int, k: int) -> dict:
+    return {"w": torch.randn(experts, n, k, generator=gen) * 0.02}
+
+
+_PLANE_MAKERS = {Q8_0: q8_0_planes, Q4_K: q4_k_planes, DENSE: dense_planes}
+
+
+@dataclass
+class Case:
+    spec: CaseSpec
+    h: torch.Tensor  # [1, T, d] fp32 holding values representable in act_dtype
+    norm_w: torch.Tensor
+    router_w: torch.Tensor
+    router_b: Optional[torch.Tensor]
+    out_norm_w: Optional[torch.Tensor]
+    gate: dict
+    up: dict
+    down: dict
+
+
+def make_case(spec: CaseSpec, tokens: Optional[int] = None, seed: Optional[int] = None) -> Case:
+    T = spec.tokens if tokens is None else tokens
+    d, f, e = spec.hidden, spec.ffn, spec.experts
+    gen = torch.Generator(device="cpu").manual_seed(spec.seed if seed is None else seed)
+    h = torch.randn(1, T, d, generator=gen)
+    if spec.act_dtype == "bf16":
+        h = h.to(torch.bfloat16).to(torch.float32)
+    router_w = torch.randn(e, d, generator=gen) * 0.02
+    router_b = None
+    if spec.router_bias == "zipf":
+        router_b = zipf_bias(gen, e)
+    elif spec.router_bias == "normal":
+        router_b = torch.randn(e, generator=gen) * 0.5
+    if spec.norm_weight == "perturbed":
+        norm_w = 1.0 + 0.1 * torch.randn(d, generator=gen)
+    else:
+        norm_w = torch.ones(d)
+    out_norm_w = None
+    if spec.out_norm:
+        if spec.norm_weight == "perturbed":
+            out_norm_w = 1.0 + 0.1 * torch.randn(d, generator=gen)
+        else:
+            out_norm_w = torch.ones(d)
+    mk = _PLANE_MAKERS[spec.kind]
+    gate = mk(gen, e, f, d)
+    up = mk(gen, e, f, d)
+    down = mk(gen, e, d, f)
+    return Case(spec, h, norm_w, router_w, router_b, out_norm_w, gate, up, down)
+
+
+def weight_bytes(kind: str, n: int, k: int) -> int:
+    """Bytes one [n, k] expert matrix occupies in its quantized planes."""
+    if kind == Q8_0:
+        return n * k // 32 * 34
+    if kind == Q4_K:
+        return n * k // 256 * 144
+    return n * k * 2  # dense weights are held as fp16 on the device
+
+
+def layer_flops(tokens: int, top_k: int, hidden: int, ffn: int) -> int:
+    """Expert-GEMM flops of one layer call: three [ffn x hidden] products per
+    (token, slot), 2 flops per multiply-add."""
+    return tokens * top_k * 3 * 2 * ffn * hidden

@@ -1,0 +1,157 @@
+"""Generate the golden fixtures in this directory by running the reference itself.
+
+Usage (needs a sharktank source checkout; iree-turbine is replaced by
+iree_stub.py, which only has to make the torch-eager path importable):
+
+    python tests/golden/make_golden.py --sharktank /path/to/sharktank
+
+Writes:
+  formats.npz      packed Q8_0 / Q4_K blocks, the planes the reference's
+                   `unpack()` produces and its `dequant()` values; outputs of
+                   the bit-unpack helpers on random bytes
+  moe_<case>.npz   outputs of sharktank's MoeBlock for the small seeded cases
+                   of shark_platform_b200.synthetic (quantized weights go
+                   through `layout.dequant()` -> DefaultPrimitiveTensor, the
+                   only way the reference can evaluate them)
+The inputs are regenerated from the seed by the tests; each fixture carries a
+SHA-256 of the inputs so that a drifting generator is detected, not ignored.
+"""
+import argparse
+import hashlib
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, HERE)
+sys.path.insert(0, ROOT)
+
+
+def digest(case) -> str:
+    m = hashlib.sha256()
+    tensors = [case.h, case.norm_w, case.router_w]
+    if case.router_b is not None:
+        tensors.append(case.router_b)
+    if case.out_norm_w is not None:
+        tensors.append(case.out_norm_w)
+    for planes in (case.gate, case.up, case.down):
+        tensors += [planes[k] for k in sorted(planes)]
+    for t in tensors:
+        m.update(t.contiguous().numpy().tobytes())
+    return m.hexdigest()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sharktank", default="/root/reference/sharktank")
+    args = ap.parse_args()
+    sys.path.insert(0, args.sharktank)
+    import iree_stub
+
+    iree_stub.install()
+    import torch.nn.functional as F
+    from sharktank.layers.mixture_of_experts_block import MoeBlock
+    from sharktank.types import DefaultPrimitiveTensor, PlanarQuantizedTensor, Theta
+    from sharktank.types.gguf_interop.layouts import Q4_K as RefQ4K, Q8_0 as RefQ8
+    from sharktank.types.layouts import (
+        BlockScaledLayout,
+        SuperBlockOffsetScaled_4_6_Layout,
+    )
+    from sharktank.types import layout_utils as lu
+
+    from shark_platform_b200 import synthetic as syn
+
+    # ---------------- formats ----------------
+    rng = np.random.default_rng(1234)
+    out = {}
+    n, k = 6, 512
+    raw8 = rng.integers(0, 256, size=(n * k // 32, 34), dtype=np.uint8)
+    sc = (np.abs(rng.standard_normal(n * k // 32)) * 0.01).astype(np.float16)
+    raw8[:, 0:2] = sc.view(np.uint8).reshape(-1, 2)
+    lay = RefQ8(raw=torch.from_numpy(raw8.reshape(-1)), shape=[n, k]).unpack()
+    out["q8_raw"] = raw8
+    out["q8_d"] = lay.d.contiguous().numpy()
+    out["q8_qs"] = lay.qs.contiguous().numpy()
+    out["q8_dequant_f16"] = lay.dequant().numpy()
+    out["q8_dequant_f32"] = lay.dequant(torch.float32).numpy()
+
+    raw4 = rng.integers(0, 256, size=(n * k // 256, 144), dtype=np.uint8)
+    dd = (np.abs(rng.standard_normal((n * k // 256, 2))) * [3e-4, 2e-3]).astype(np.float16)
+    raw4[:, 0:4] = dd.view(np.uint8).reshape(-1, 4)
+    lay4 = RefQ4K(raw=torch.from_numpy(raw4.reshape(-1)), shape=[n, k]).unpack()
+    out["q4k_raw"] = raw4
+    for name, t in lay4.planes.items():
+        out["q4k_" + name] = t.contiguous().numpy()
+    out["q4k_sb_scales"] = lay4.sb_scales.numpy()
+    out["q4k_sb_mins"] = lay4.sb_mins.numpy()
+    out["q4k_qs_i8"] = lay4.qs.numpy()
+    out["q4k_dequant_f16"] = lay4.dequant().numpy()
+
+    b = rng.integers(0, 256, size=(5, 16), dtype=np.uint8)
+    tb = torch.from_numpy(b)
+    out["bits_in"] = b
+    out["bits_linearize_i4"] = lu.linearize_interleaved_i4_block(tb).numpy()
+    out["bits_interleave_i4"] = lu.interleave_linear_i4_block(tb).numpy()
+    out["bits_i4_unsigned"] = lu.promote_linear_i4_block_to_i8(tb).numpy()
+    out["bits_i4_signed"] = lu.promote_linear_i4_block_to_i8(tb, signed=True).numpy()
+    out["bits_i2"] = lu.promote_linear_i2_block_to_i8(tb).numpy()
+    out["bits_i6"] = lu.promote_linear_i6_block_to_i8(tb[:, :4], tb[:, 8:16]).numpy()
+    np.savez_compressed(os.path.join(HERE, "formats.npz"), **out)
+    print("formats.npz written")
+
+    # ---------------- MoE layer ----------------
+    def ref_weight(kind, planes, shape):
+        if kind == syn.Q8_0:
+            lay = BlockScaledLayout(shape, planes["d"], planes["qs"])
+        elif kind == syn.Q4_K:
+            lay = SuperBlockOffsetScaled_4_6_Layout(shape, **planes)
+        else:
+            return DefaultPrimitiveTensor(data=planes["w"])
+        qt = PlanarQuantizedTensor(shape=shape, layout=lay)
+        return DefaultPrimitiveTensor(data=qt.unpack().dequant())
+
+    for name in ["toy", "small_q8", "small_q4k", "small_grok", "small_top4", "small_dense"]:
+        spec = syn.CASES[name]
+        case = syn.make_case(spec)
+        e, f, d = spec.experts, spec.ffn, spec.hidden
+        tree = {
+            "ffn_gate_inp": {"weight": DefaultPrimitiveTensor(data=case.router_w)},
+            "ffn_norm": {"weight": DefaultPrimitiveTensor(data=case.norm_w)},
+            "ffn_gate_exps": {"weight": ref_weight(spec.kind, case.gate, [e, f, d])},
+            "ffn_up_exps": {"weight": ref_weight(spec.kind, case.up, [e, f, d])},
+            "ffn_down_exps": {"weight": ref_weight(spec.kind, case.down, [e, d, f])},
+        }
+        if case.router_b is not None:
+            tree["ffn_gate_inp"]["bias"] = DefaultPrimitiveTensor(data=case.router_b)
+        if case.out_norm_w is not None:
+            tree["layer_output_norm"] = {"weight": DefaultPrimitiveTensor(data=case.out_norm_w)}
+        act = F.silu if spec.activation == "silu" else F.gelu
+        block = MoeBlock(Theta(tree), e, spec.top_k, spec.eps, moe_activation=act)
+
+        captured = {}
+        orig = block.experts.forward
+
+        def spy(h, experts, expert_gate):
+            captured["xn"] = h.clone()
+            captured["experts"] = experts.clone()
+            captured["gate"] = expert_gate.clone()
+            return orig(h, experts, expert_gate)
+
+        block.experts.forward = spy
+        y = block(case.h)
+        np.savez_compressed(
+            os.path.join(HERE, f"moe_{name}.npz"),
+            y=y.numpy(),
+            experts=captured["experts"].numpy(),
+            gate=captured["gate"].numpy(),
+            xn=captured["xn"].numpy(),
+            digest=np.array(digest(case)),
+        )
+        print(f"moe_{name}.npz written  |y|={float(y.abs().mean()):.4f}")
+
+
+if __name__ == "__main__":
+    main()
