@@ -1,0 +1,189 @@
+/*
+ * b200moe — C ABI of the B200 (sm_100a) mixture-of-experts FFN library.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on the
+ * given CUDA stream (a cudaStream_t passed as void*; NULL = default stream) and
+ * returns without synchronising.  Return value: 0 on success, a negative
+ * B200MOE_ERR_* code otherwise; b200moe_last_error() gives the message of the
+ * calling thread's last failure.  The library never aborts the process and,
+ * unless an entry point says otherwise, allocates no device memory: the caller
+ * owns every buffer, including the workspace.
+ *
+ * Each declaration names the piece of sharktank (paths relative to the
+ * sharktank project root) whose torch-eager behaviour it replaces.
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_OK 0
+#define B200MOE_ERR_INVALID (-1)     /* bad argument / unsupported shape */
+#define B200MOE_ERR_CUDA (-2)        /* a CUDA runtime or driver call failed */
+#define B200MOE_ERR_WORKSPACE (-3)   /* workspace too small */
+#define B200MOE_ERR_DEVICE (-4)      /* a kernel reported a bounded-wait timeout or a bounds error */
+
+/* Weight layouts.  Q8_0 and Q4_K consume the *planar* planes of sharktank's
+ * BlockScaledLayout (types/layouts.py:194-299) and
+ * SuperBlockOffsetScaled_4_6_Layout (types/layouts.py:360-530) in place. */
+enum {
+  B200MOE_LAYOUT_Q8_0 = 0, /* qs: int8 [E,N,K]; d: fp16 [E,N,K/32] */
+  B200MOE_LAYOUT_Q4_K = 1, /* qs: u8 [E,N,K/2] (planar nibbles); sub: half2 [E,N,K/32] from b200moe_q4k_prepare */
+  B200MOE_LAYOUT_F16 = 2   /* qs: fp16 [E,N,K] dense */
+};
+
+enum { B200MOE_ACT_SILU = 0, B200MOE_ACT_GELU = 1 }; /* F.silu | F.gelu (erf) */
+enum { B200MOE_DT_F32 = 0, B200MOE_DT_F16 = 1, B200MOE_DT_BF16 = 2 };
+enum { B200MOE_REGIME_AUTO = 0, B200MOE_REGIME_STREAM = 1, B200MOE_REGIME_TENSOR = 2 };
+
+/* One stacked expert weight tensor `ffn_{gate,up,down}_exps.weight`,
+ * logical shape [experts, rows, cols] with cols (the reduction dim) innermost
+ * (layers/ffn_moe_block.py:32-34). */
+typedef struct {
+  int32_t layout;
+  int32_t experts;
+  int32_t rows;
+  int32_t cols;
+  const void* qs;  /* quantised values (or dense fp16 values) */
+  const void* d;   /* Q8_0: per-block fp16 scales; otherwise NULL */
+  const void* sub; /* Q4_K: per-sub-block (scale, min) half2 pairs; otherwise NULL */
+} b200moe_weight_t;
+
+/* Parameters of one MoeBlock (layers/mixture_of_experts_block.py:31-62). */
+typedef struct {
+  int32_t hidden;      /* d */
+  int32_t ffn;         /* F */
+  int32_t experts;     /* E (<= 64) */
+  int32_t top_k;       /* expert_used_count (<= 8) */
+  int32_t activation;  /* B200MOE_ACT_* */
+  float rms_epsilon;
+  const float* ffn_norm_weight;          /* [d]   ffn_norm.weight */
+  const float* router_weight;            /* [E,d] ffn_gate_inp.weight */
+  const float* router_bias;              /* [E]   ffn_gate_inp.bias or NULL */
+  const float* layer_output_norm_weight; /* [d]   layer_output_norm.weight or NULL */
+  b200moe_weight_t gate, up, down;
+  /* Expert parallelism: this process owns experts [expert_begin, expert_begin+gate.experts). */
+  int32_t expert_begin;
+} b200moe_layer_t;
+
+const char* b200moe_version(void);
+const char* b200moe_last_error(void);
+
+/* Reads and clears the device status word that kernels set when a bounded
+ * wait gives up or an index check fails; synchronises the stream.  0 = clean. */
+int b200moe_device_status(void* stream, int32_t* status_out);
+
+/* layout.dequant() of one weight tensor, bit-exact (types/layouts.py:274-290
+ * for Q8_0: fp16(d*q) or the exact fp32 product; types/layouts.py:505-517 for
+ * Q4_K: fp16 with one rounding per operation).  out: [E,N,K] of out_dtype
+ * (B200MOE_DT_F16 or B200MOE_DT_F32; Q4_K in F32 is the fp16 value widened). */
+int b200moe_dequant(const b200moe_weight_t* w, int out_dtype, void* out, void* stream);
+
+/* Q4_K: fold the planar 6-bit sub-scale / sub-min planes and the fp16 d / dmin
+ * (SuperBlockOffsetScaled_4_6_Layout planes, types/layouts.py:421-470;
+ * layout_utils.py:104-113 for the 6-bit combine) into per-sub-block half2
+ * (fp16(d*sc), fp16(dmin*m)) — the first two roundings of the reference
+ * dequant.  blocks = E*N*K/256; sub_out: half2 [blocks*8]. */
+int b200moe_q4k_prepare(const void* d, const void* dmin, const uint8_t* sb_scales_high,
+                        const uint8_t* sb_scales_low, const uint8_t* sb_mins_high,
+                        const uint8_t* sb_mins_low, int64_t blocks, void* sub_out, void* stream);
+
+/* Packed GGUF blocks -> the planar planes above (types/gguf_interop/layouts.py:
+ * 51-60 Q8_0.unpack; :112-153 Q4_K.unpack with _unpack_gguf_i6_scale_mins
+ * :163-217).  raw: blocks*34 (Q8_0) or blocks*144 (Q4_K) bytes. */
+int b200moe_gguf_unpack_q8_0(const uint8_t* raw, int64_t blocks, void* d_out, int8_t* qs_out,
+                             void* stream);
+int b200moe_gguf_unpack_q4_k(const uint8_t* raw, int64_t blocks, void* d_out, void* dmin_out,
+                             uint8_t* sb_scales_high, uint8_t* sb_scales_low,
+                             uint8_t* sb_mins_high, uint8_t* sb_mins_low, uint8_t* qs_out,
+                             void* stream);
+
+/* Router: RMSNormLayer (layers/norm.py:34-41, ops/default_impls.py:402-408),
+ * ffn_gate_inp linear (ops/default_impls.py:328-341), fp32 softmax, top-k and
+ * renormalisation (layers/mixture_of_experts_block.py:66-83).
+ * h: [T,d] of h_dtype (F32 or BF16).  Outputs: xn fp16 [T,d] (the normalised
+ * activations as expert-GEMM operand), experts int32 [T,k] in descending
+ * probability order, gates fp32 [T,k]. */
+int b200moe_router(const void* h, int h_dtype, int32_t tokens, const b200moe_layer_t* layer,
+                   void* xn_out, int32_t* experts_out, float* gates_out, void* stream);
+
+/* Token permutation (no reference function; definition: pairs p = token*k+slot
+ * stably sorted by expert id).  experts: int32 [pairs] with global expert ids;
+ * pairs whose expert lies outside [expert_begin, expert_begin+experts_local)
+ * are dropped.  counts [E_local], seg_offsets [E_local+1], perm [pairs]
+ * (sorted position -> pair), inv [pairs] (pair -> sorted position or -1). */
+int b200moe_route_plan(const int32_t* experts, int32_t pairs, int32_t expert_begin,
+                       int32_t experts_local, int32_t* counts, int32_t* seg_offsets,
+                       int32_t* perm, int32_t* inv, void* stream);
+
+/* xs[pos,:] = xn[perm[pos] / top_k,:] for pos < seg_offsets[E_local]: the rows
+ * each expert multiplies, contiguous per expert (replaces the per-token weight
+ * gather `weights[experts]` of layers/ffn_moe_block.py:37-41). */
+int b200moe_permute_rows(const void* xn, const int32_t* perm, const int32_t* seg_offsets,
+                         int32_t experts_local, int32_t pairs, int32_t top_k, int32_t hidden,
+                         int32_t kperm, void* xs_out, void* stream);
+
+/* Whether the expert-GEMM kernels for this weight layout want their input
+ * columns in the interleaved order 0,4,1,5,2,6,3,7 within every group of eight
+ * (1) or in natural order (0).  Pass the value to b200moe_permute_rows (for the
+ * gate/up input) and to b200moe_gate_up (for its output, the down input). */
+int b200moe_kperm(int layout, int regime, int32_t max_segment);
+
+/* act(xs W_gate[e]^T) * (xs W_up[e]^T) per expert segment: the "mk,menk->men"
+ * einsums of pre_matmul_gather, the activation and the product
+ * (layers/ffn_moe_block.py:60-71; ops/default_impls.py:72-81).  xs fp16
+ * [pairs,d] sorted rows; a_out fp16 [pairs,F].  max_segment: an upper bound on
+ * the rows of any one expert (the token count when experts are not sharded). */
+int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
+                    int32_t max_segment, const b200moe_weight_t* gate,
+                    const b200moe_weight_t* up, int activation, int regime, int32_t out_kperm,
+                    void* a_out, void* stream);
+
+/* Number of k-split partial sums b200moe_down writes for these arguments. */
+int b200moe_down_ksplit(const b200moe_weight_t* down, int32_t pairs, int32_t max_segment,
+                        int regime);
+
+/* Down projection per expert segment: the "mek,menk->men" einsum
+ * (layers/ffn_moe_block.py:70-72; ops/default_impls.py:84-94).  a fp16
+ * [pairs,F]; d_out fp32 [ksplit, pairs, d] partial sums with ksplit =
+ * b200moe_down_ksplit(...) (the combine adds the partials in index order). */
+int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32_t max_segment,
+                 const b200moe_weight_t* down, int regime, float* d_out, void* stream);
+
+/* y[t] = h[t] + norm?( sum_slot gates[t,slot] * D[inv[t*k+slot]] ): the
+ * "me,men->men" scaling and torch.sum over slots (layers/ffn_moe_block.py:
+ * 73-74), the optional layer_output_norm and the residual
+ * (layers/mixture_of_experts_block.py:86-90).  Pairs with inv < 0 (experts of
+ * another rank) contribute nothing.  If add_residual is 0 the result is the
+ * un-normalised partial sum (used under expert parallelism). */
+int b200moe_combine(const float* d_partials, int32_t ksplit, int32_t pairs, const int32_t* inv,
+                    const float* gates, const void* h, int h_dtype, int32_t tokens,
+                    const b200moe_layer_t* layer, int add_residual, void* y_out, int y_dtype,
+                    void* stream);
+
+/* Bytes of workspace b200moe_layer_forward needs for up to `tokens` tokens. */
+size_t b200moe_workspace_bytes(const b200moe_layer_t* layer, int32_t tokens);
+
+/* Whole MoeBlock.forward (layers/mixture_of_experts_block.py:64-90) on one
+ * device: router -> route plan -> permute -> gate/up -> down -> combine.
+ * h, y: [T,d] of io_dtype (F32 or BF16).  experts_out / gates_out may be NULL. */
+int b200moe_layer_forward(const b200moe_layer_t* layer, const void* h, void* y, int io_dtype,
+                          int32_t tokens, int regime, void* workspace, size_t workspace_bytes,
+                          int32_t* experts_out, float* gates_out, void* stream);
+
+/* Same call with host buffers: copies h to the device, runs the layer and
+ * copies y back on `stream` (pinned host memory makes the copies asynchronous).
+ * dev_io: device scratch of at least 2*T*d*sizeof(io_dtype) bytes. */
+int b200moe_layer_forward_host(const b200moe_layer_t* layer, const void* h_host, void* y_host,
+                               int io_dtype, int32_t tokens, int regime, void* dev_io,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

@@ -1,0 +1,577 @@
+// Router, route plan, row permutation, combine, reference dequantisation and
+// GGUF block unpacking.  All HBM-bound or latency-bound helpers around the two
+// expert-GEMM kernels.
+#include "common.cuh"
+
+namespace b200moe {
+
+// ------------------------------------------------------------------ router
+// One warp per token.  RMS norm in fp32 (x * 1/sqrt(mean(x^2)+eps), then the
+// norm weight), router logits from the fp32 normalised row, fp32 softmax,
+// top-k by descending probability (ties: lowest expert id) and renormalised
+// gates.  The normalised row is written as fp16 for the expert products.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+constexpr int ROUTER_WARPS = 8;
+constexpr int MAX_EXPERTS = 64;
+constexpr int MAX_TOPK = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_kernel(const T* __restrict__ h, int tokens, int d, int E, int k, float eps,
+              const float* __restrict__ norm_w, const float* __restrict__ rw,
+              const float* __restrict__ rb, __half* __restrict__ xn_out,
+              int32_t* __restrict__ experts_out, float* __restrict__ gates_out) {
+  __shared__ float s_logit[ROUTER_WARPS][MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTER_WARPS + warp;
+  if (t >= tokens) return;
+  const T* row = h + static_cast<size_t>(t) * d;
+
+  float ss = 0.f;
+  for (int j = lane * 8; j < d; j += 256) {
+    float v[8];
+    load8<T>(row + j, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float rstd = 1.0f / sqrtf(ss / static_cast<float>(d) + eps);
+
+  for (int e0 = 0; e0 < E; e0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int j = lane * 8; j < d; j += 256) {
+      float v[8], w[8];
+      load8<T>(row + j, v);
+      load8<float>(norm_w + j, w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = w[i] * (v[i] * rstd);
+      if (e0 == 0) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          packed[i] = h2_as_u32(__halves2half2(to_half_sat(v[2 * i]), to_half_sat(v[2 * i + 1])));
+        *reinterpret_cast<uint4*>(xn_out + static_cast<size_t>(t) * d + j) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (e0 + e < E) {
+          float r[8];
+          load8<float>(rw + static_cast<size_t>(e0 + e) * d + j, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[e] = fmaf(v[i], r[i], acc[e]);
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+      if (lane == 0 && e0 + e < E) s_logit[warp][e0 + e] = acc[e] + (rb ? rb[e0 + e] : 0.f);
+    }
+  }
+  __syncwarp();
+
+  // softmax over E <= 64: lane owns experts lane and lane+32
+  const float NEG = -INFINITY;
+  float l0 = lane < E ? s_logit[warp][lane] : NEG;
+  float l1 = lane + 32 < E ? s_logit[warp][lane + 32] : NEG;
+  float mx = fmaxf(l0, l1);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float p0 = lane < E ? expf(l0 - mx) : 0.f;
+  float p1 = lane + 32 < E ? expf(l1 - mx) : 0.f;
+  float sum = p0 + p1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  p0 = lane < E ? p0 / sum : -1.f;
+  p1 = lane + 32 < E ? p1 / sum : -1.f;
+
+  float sel_p[MAX_TOPK];
+  int sel_i[MAX_TOPK];
+  float gsum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_TOPK; ++i) {
+    if (i < k) {
+      float bp = p0;
+      int bi = lane;
+      if (p1 > bp) { bp = p1; bi = lane + 32; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float op = __shfl_xor_sync(0xffffffffu, bp, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (op > bp || (op == bp && oi < bi)) { bp = op; bi = oi; }
+      }
+      sel_p[i] = bp;
+      sel_i[i] = bi;
+      gsum += bp;
+      if (bi == lane) p0 = -1.f;
+      if (bi == lane + 32) p1 = -1.f;
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < MAX_TOPK; ++i) {
+      if (i < k) {
+        experts_out[static_cast<size_t>(t) * k + i] = sel_i[i];
+        gates_out[static_cast<size_t>(t) * k + i] = sel_p[i] / gsum;
+      }
+    }
+  }
+}
+
+int launch_router(const void* h, int h_dtype, int tokens, const b200moe_layer_t* L, void* xn,
+                  int32_t* experts, float* gates, cudaStream_t st) {
+  B200_REQUIRE(L->hidden % 256 == 0, "router: hidden (%d) must be a multiple of 256", L->hidden);
+  B200_REQUIRE(L->experts >= 1 && L->experts <= MAX_EXPERTS, "router: experts (%d) must be 1..64",
+               L->experts);
+  B200_REQUIRE(L->top_k >= 1 && L->top_k <= MAX_TOPK && L->top_k <= L->experts,
+               "router: top_k (%d) must be 1..min(8, experts)", L->top_k);
+  if (tokens == 0) return B200MOE_OK;
+  dim3 grid((tokens + ROUTER_WARPS - 1) / ROUTER_WARPS), block(ROUTER_WARPS * 32);
+  if (h_dtype == B200MOE_DT_F32) {
+    router_kernel<float><<<grid, block, 0, st>>>(
+        static_cast<const float*>(h), tokens, L->hidden, L->experts, L->top_k, L->rms_epsilon,
+        L->ffn_norm_weight, L->router_weight, L->router_bias, static_cast<__half*>(xn), experts,
+        gates);
+  } else if (h_dtype == B200MOE_DT_BF16) {
+    router_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(h), tokens, L->hidden, L->experts, L->top_k,
+        L->rms_epsilon, L->ffn_norm_weight, L->router_weight, L->router_bias,
+        static_cast<__half*>(xn), experts, gates);
+  } else {
+    B200_REQUIRE(false, "router: activations must be fp32 or bf16");
+  }
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+// -------------------------------------------------------------- route plan
+// Stable counting sort of (token, slot) pairs by expert in one CTA: a shared
+// histogram gives the segment offsets, then each 1024-pair chunk ranks its
+// pairs with warp match/ballot masks and a per-expert scan over the 32 warps.
+constexpr int PLAN_THREADS = 1024;
+
+__global__ void __launch_bounds__(PLAN_THREADS)
+route_plan_kernel(const int32_t* __restrict__ experts, int pairs, int e_begin, int E,
+                  int32_t* __restrict__ counts, int32_t* __restrict__ seg,
+                  int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+  __shared__ int s_total[MAX_EXPERTS];
+  __shared__ int s_run[MAX_EXPERTS];
+  __shared__ int s_warp[32][MAX_EXPERTS];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < MAX_EXPERTS) s_total[tid] = 0;
+  __syncthreads();
+  for (int p = tid; p < pairs; p += PLAN_THREADS) {
+    const int le = experts[p] - e_begin;
+    if (le >= 0 && le < E) atomicAdd(&s_total[le], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      seg[e] = run;
+      counts[e] = s_total[e];
+      s_run[e] = run;
+      run += s_total[e];
+    }
+    seg[E] = run;
+  }
+  __syncthreads();
+  for (int base = 0; base < pairs; base += PLAN_THREADS) {
+    const int p = base + tid;
+    int le = -1;
+    if (p < pairs) {
+      le = experts[p] - e_begin;
+      if (le < 0 || le >= E) le = -1;
+    }
+    for (int e = lane; e < E; e += 32) s_warp[warp][e] = 0;
+    __syncwarp();
+    const unsigned peers = __match_any_sync(0xffffffffu, le);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (le >= 0 && rank == 0) s_warp[warp][le] = __popc(peers);
+    __syncthreads();
+    if (tid < E) {
+      int run = s_run[tid];
+      for (int w = 0; w < 32; ++w) {
+        const int c = s_warp[w][tid];
+        s_warp[w][tid] = run;
+        run += c;
+      }
+      s_run[tid] = run;
+    }
+    __syncthreads();
+    if (p < pairs) {
+      if (le >= 0) {
+        const int pos = s_warp[warp][le] + rank;
+        perm[pos] = p;
+        inv[p] = pos;
+      } else {
+        inv[p] = -1;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+int launch_route_plan(const int32_t* experts, int pairs, int e_begin, int E, int32_t* counts,
+                      int32_t* seg, int32_t* perm, int32_t* inv, cudaStream_t st) {
+  B200_REQUIRE(E >= 1 && E <= MAX_EXPERTS, "route_plan: local experts (%d) must be 1..64", E);
+  B200_REQUIRE(pairs >= 0, "route_plan: negative pair count");
+  route_plan_kernel<<<1, PLAN_THREADS, 0, st>>>(experts, pairs, e_begin, E, counts, seg, perm, inv);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+// ------------------------------------------------------------ permute rows
+// xs[pos,:] = xn[perm[pos]/k,:].  With kperm the eight halves of every 16-byte
+// group are written in the order 0,4,1,5,2,6,3,7 — the order in which the Q4_K
+// kernels pull nibble pairs out of a 32-bit word.
+__global__ void __launch_bounds__(128)
+permute_rows_kernel(const uint4* __restrict__ xn, const int32_t* __restrict__ perm,
+                    const int32_t* __restrict__ seg, int E, int k, int vec_per_row, int kperm,
+                    uint4* __restrict__ xs) {
+  const int pos = blockIdx.x;
+  if (pos >= seg[E]) return;
+  const int tok = perm[pos] / k;
+  const uint4* src = xn + static_cast<size_t>(tok) * vec_per_row;
+  uint4* dst = xs + static_cast<size_t>(pos) * vec_per_row;
+  for (int j = threadIdx.x; j < vec_per_row; j += blockDim.x) {
+    uint4 v = src[j];
+    if (kperm) {
+      uint4 o;
+      o.x = __byte_perm(v.x, v.z, 0x5410);  // (h0, h4)
+      o.y = __byte_perm(v.x, v.z, 0x7632);  // (h1, h5)
+      o.z = __byte_perm(v.y, v.w, 0x5410);  // (h2, h6)
+      o.w = __byte_perm(v.y, v.w, 0x7632);  // (h3, h7)
+      v = o;
+    }
+    dst[j] = v;
+  }
+}
+
+int launch_permute_rows(const void* xn, const int32_t* perm, const int32_t* seg, int E, int pairs,
+                        int k, int d, int kperm, void* xs, cudaStream_t st) {
+  B200_REQUIRE(d % 8 == 0, "permute_rows: hidden must be a multiple of 8");
+  if (pairs == 0) return B200MOE_OK;
+  permute_rows_kernel<<<pairs, 128, 0, st>>>(static_cast<const uint4*>(xn), perm, seg, E, k,
+                                             d / 8, kperm, static_cast<uint4*>(xs));
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+// ----------------------------------------------------------------- combine
+// One CTA per token: sum over slots (in slot order) of gate * (sum of the
+// k-split partials of the pair's down-projection row), optional output RMS
+// norm, residual add.
+template <typename T>
+__device__ __forceinline__ float load1(const T* p);
+template <>
+__device__ __forceinline__ float load1<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float load1<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+template <typename T>
+__device__ __forceinline__ void store1(T* p, float v);
+template <>
+__device__ __forceinline__ void store1<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store1<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16_rn(v);
+}
+
+constexpr int COMBINE_THREADS = 256;
+
+template <typename TH, typename TY>
+__global__ void __launch_bounds__(COMBINE_THREADS)
+combine_kernel(const float* __restrict__ dpart, int ksplit, size_t part_stride,
+               const int32_t* __restrict__ inv, const float* __restrict__ gates,
+               const TH* __restrict__ h, int d, int k, const float* __restrict__ out_norm_w,
+               float eps, int add_residual, TY* __restrict__ y) {
+  extern __shared__ float s_row[];
+  __shared__ float s_red[COMBINE_THREADS / 32];
+  const int t = blockIdx.x;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < d; j += COMBINE_THREADS) {
+    float acc = 0.f;
+    for (int s = 0; s < k; ++s) {
+      const int pos = inv[static_cast<size_t>(t) * k + s];
+      if (pos < 0) continue;
+      float v = 0.f;
+      for (int c = 0; c < ksplit; ++c)
+        v += dpart[c * part_stride + static_cast<size_t>(pos) * d + j];
+      acc += gates[static_cast<size_t>(t) * k + s] * v;
+    }
+    s_row[j] = acc;
+    ss = fmaf(acc, acc, ss);
+  }
+  float scale = 1.f;
+  if (out_norm_w != nullptr && add_residual) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < COMBINE_THREADS / 32; ++w) tot += s_red[w];
+    scale = 1.0f / sqrtf(tot / static_cast<float>(d) + eps);
+  }
+  for (int j = threadIdx.x; j < d; j += COMBINE_THREADS) {
+    float v = s_row[j];
+    if (add_residual) {
+      if (out_norm_w != nullptr) v = out_norm_w[j] * (v * scale);
+      v += load1<TH>(h + static_cast<size_t>(t) * d + j);
+    }
+    store1<TY>(y + static_cast<size_t>(t) * d + j, v);
+  }
+}
+
+int launch_combine(const float* dpart, int ksplit, int pairs, const int32_t* inv,
+                   const float* gates, const void* h, int h_dtype, int tokens,
+                   const b200moe_layer_t* L, int add_residual, void* y, int y_dtype,
+                   cudaStream_t st) {
+  if (tokens == 0) return B200MOE_OK;
+  const int d = L->hidden, k = L->top_k;
+  const size_t smem = static_cast<size_t>(d) * sizeof(float);
+  B200_REQUIRE(smem <= 48 * 1024, "combine: hidden (%d) too large", d);
+  const size_t stride = static_cast<size_t>(pairs) * d;
+  dim3 grid(tokens), block(COMBINE_THREADS);
+#define LAUNCH(TH, TY)                                                                         \
+  combine_kernel<TH, TY><<<grid, block, smem, st>>>(dpart, ksplit, stride, inv, gates,         \
+                                                    static_cast<const TH*>(h), d, k,           \
+                                                    L->layer_output_norm_weight,               \
+                                                    L->rms_epsilon, add_residual,              \
+                                                    static_cast<TY*>(y))
+  if (h_dtype == B200MOE_DT_F32 && y_dtype == B200MOE_DT_F32) {
+    LAUNCH(float, float);
+  } else if (h_dtype == B200MOE_DT_BF16 && y_dtype == B200MOE_DT_BF16) {
+    LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  } else if (h_dtype == B200MOE_DT_BF16 && y_dtype == B200MOE_DT_F32) {
+    LAUNCH(__nv_bfloat16, float);
+  } else {
+    B200_REQUIRE(false, "combine: unsupported dtype pair (%d, %d)", h_dtype, y_dtype);
+  }
+#undef LAUNCH
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+// ----------------------------------------------------- reference dequantise
+template <typename TO>
+__global__ void dequant_q8_kernel(const int8_t* __restrict__ qs, const __half* __restrict__ d,
+                                  size_t n, TO* __restrict__ out) {
+  const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  const __half scale = d[i >> 5];
+  if constexpr (sizeof(TO) == 2) {
+    out[i] = __hmul(scale, __int2half_rn(qs[i]));
+  } else {
+    out[i] = __half2float(scale) * static_cast<float>(qs[i]);
+  }
+}
+
+template <typename TO>
+__global__ void dequant_q4k_kernel(const uint8_t* __restrict__ qs, const __half2* __restrict__ sub,
+                                   size_t n, TO* __restrict__ out) {
+  const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  const uint8_t b = qs[i >> 1];
+  const int q = (i & 1) ? (b >> 4) : (b & 0xF);
+  const __half2 sm = sub[i >> 5];
+  const __half w = __hsub(__hmul(__low2half(sm), __int2half_rn(q)), __high2half(sm));
+  if constexpr (sizeof(TO) == 2) {
+    out[i] = w;
+  } else {
+    out[i] = __half2float(w);
+  }
+}
+
+template <typename TO>
+__global__ void dequant_f16_kernel(const __half* __restrict__ w, size_t n, TO* __restrict__ out) {
+  const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  if constexpr (sizeof(TO) == 2) {
+    out[i] = w[i];
+  } else {
+    out[i] = __half2float(w[i]);
+  }
+}
+
+int launch_dequant(const b200moe_weight_t* w, int out_dtype, void* out, cudaStream_t st) {
+  B200_REQUIRE(out_dtype == B200MOE_DT_F16 || out_dtype == B200MOE_DT_F32,
+               "dequant: out_dtype must be fp16 or fp32");
+  const size_t n = static_cast<size_t>(w->experts) * w->rows * w->cols;
+  if (n == 0) return B200MOE_OK;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((n + threads - 1) / threads);
+  const bool f16 = out_dtype == B200MOE_DT_F16;
+  switch (w->layout) {
+    case B200MOE_LAYOUT_Q8_0:
+      B200_REQUIRE(w->cols % 32 == 0, "dequant: Q8_0 needs cols %% 32 == 0");
+      if (f16)
+        dequant_q8_kernel<__half><<<blocks, threads, 0, st>>>(
+            static_cast<const int8_t*>(w->qs), static_cast<const __half*>(w->d), n,
+            static_cast<__half*>(out));
+      else
+        dequant_q8_kernel<float><<<blocks, threads, 0, st>>>(
+            static_cast<const int8_t*>(w->qs), static_cast<const __half*>(w->d), n,
+            static_cast<float*>(out));
+      break;
+    case B200MOE_LAYOUT_Q4_K:
+      B200_REQUIRE(w->cols % 256 == 0, "dequant: Q4_K needs cols %% 256 == 0");
+      if (f16)
+        dequant_q4k_kernel<__half><<<blocks, threads, 0, st>>>(
+            static_cast<const uint8_t*>(w->qs), static_cast<const __half2*>(w->sub), n,
+            static_cast<__half*>(out));
+      else
+        dequant_q4k_kernel<float><<<blocks, threads, 0, st>>>(
+            static_cast<const uint8_t*>(w->qs), static_cast<const __half2*>(w->sub), n,
+            static_cast<float*>(out));
+      break;
+    case B200MOE_LAYOUT_F16:
+      if (f16)
+        dequant_f16_kernel<__half><<<blocks, threads, 0, st>>>(static_cast<const __half*>(w->qs),
+                                                               n, static_cast<__half*>(out));
+      else
+        dequant_f16_kernel<float><<<blocks, threads, 0, st>>>(static_cast<const __half*>(w->qs),
+                                                              n, static_cast<float*>(out));
+      break;
+    default:
+      B200_REQUIRE(false, "dequant: unknown layout %d", w->layout);
+  }
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+// --------------------------------------------------------- Q4_K scale fold
+// One thread per super-block: the eight 6-bit sub-scales / sub-mins
+// (low nibble plane | 2-bit high plane << 4) times d / dmin, each product
+// rounded once to fp16.
+__global__ void q4k_prepare_kernel(const __half* __restrict__ d, const __half* __restrict__ dmin,
+                                   const uint8_t* __restrict__ sh, const uint8_t* __restrict__ sl,
+                                   const uint8_t* __restrict__ mh, const uint8_t* __restrict__ ml,
+                                   long long blocks, __half2* __restrict__ sub) {
+  const long long b = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (b >= blocks) return;
+  const __half dd = d[b], dm = dmin[b];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int sc = ((sl[b * 4 + (i >> 1)] >> ((i & 1) * 4)) & 0xF) |
+                   (((sh[b * 2 + (i >> 2)] >> ((i & 3) * 2)) & 3) << 4);
+    const int mn = ((ml[b * 4 + (i >> 1)] >> ((i & 1) * 4)) & 0xF) |
+                   (((mh[b * 2 + (i >> 2)] >> ((i & 3) * 2)) & 3) << 4);
+    sub[b * 8 + i] = __halves2half2(__hmul(dd, __int2half_rn(sc)), __hmul(dm, __int2half_rn(mn)));
+  }
+}
+
+int launch_q4k_prepare(const void* d, const void* dmin, const uint8_t* sh, const uint8_t* sl,
+                       const uint8_t* mh, const uint8_t* ml, long long blocks, void* sub,
+                       cudaStream_t st) {
+  if (blocks == 0) return B200MOE_OK;
+  const int threads = 256;
+  q4k_prepare_kernel<<<static_cast<unsigned>((blocks + threads - 1) / threads), threads, 0, st>>>(
+      static_cast<const __half*>(d), static_cast<const __half*>(dmin), sh, sl, mh, ml, blocks,
+      static_cast<__half2*>(sub));
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+// ------------------------------------------------------------- GGUF unpack
+// Q8_0 file block: fp16 scale + 32 int8.  One thread per quant.
+__global__ void gguf_q8_kernel(const uint8_t* __restrict__ raw, long long blocks,
+                               uint16_t* __restrict__ d, int8_t* __restrict__ qs) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= blocks * 32) return;
+  const long long b = i >> 5;
+  const int j = static_cast<int>(i & 31);
+  const uint8_t* blk = raw + b * 34;
+  qs[i] = static_cast<int8_t>(blk[2 + j]);
+  if (j == 0) d[b] = static_cast<uint16_t>(blk[0]) | (static_cast<uint16_t>(blk[1]) << 8);
+}
+
+// Q4_K file super-block (144 B): d, dmin, 12 bytes of 6-bit fields, 128 bytes
+// of nibbles.  One thread per super-block writes the planar planes.
+__global__ void gguf_q4k_kernel(const uint8_t* __restrict__ raw, long long blocks,
+                                uint16_t* __restrict__ d, uint16_t* __restrict__ dmin,
+                                uint8_t* __restrict__ sh, uint8_t* __restrict__ sl,
+                                uint8_t* __restrict__ mh, uint8_t* __restrict__ ml,
+                                uint8_t* __restrict__ qs) {
+  const long long b = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (b >= blocks) return;
+  const uint8_t* blk = raw + b * 144;
+  d[b] = static_cast<uint16_t>(blk[0]) | (static_cast<uint16_t>(blk[1]) << 8);
+  dmin[b] = static_cast<uint16_t>(blk[2]) | (static_cast<uint16_t>(blk[3]) << 8);
+  const uint8_t* s = blk + 4;
+  uint8_t sc[8], mn[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    sc[i] = s[i] & 63;
+    mn[i] = s[i + 4] & 63;
+    sc[i + 4] = (s[i + 8] & 0xF) | ((s[i] >> 6) << 4);
+    mn[i + 4] = (s[i + 8] >> 4) | ((s[i + 4] >> 6) << 4);
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    sl[b * 4 + j] = (sc[2 * j] & 0xF) | ((sc[2 * j + 1] & 0xF) << 4);
+    ml[b * 4 + j] = (mn[2 * j] & 0xF) | ((mn[2 * j + 1] & 0xF) << 4);
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    sh[b * 2 + j] = (sc[4 * j] >> 4) | ((sc[4 * j + 1] >> 4) << 2) | ((sc[4 * j + 2] >> 4) << 4) |
+                    ((sc[4 * j + 3] >> 4) << 6);
+    mh[b * 2 + j] = (mn[4 * j] >> 4) | ((mn[4 * j + 1] >> 4) << 2) | ((mn[4 * j + 2] >> 4) << 4) |
+                    ((mn[4 * j + 3] >> 4) << 6);
+  }
+  const uint8_t* q = blk + 16;
+  uint8_t* o = qs + b * 128;
+  for (int g = 0; g < 4; ++g) {
+    for (int i = 0; i < 16; ++i) {
+      const uint8_t a = q[32 * g + 2 * i], c = q[32 * g + 2 * i + 1];
+      o[(2 * g) * 16 + i] = (a & 0xF) | ((c & 0xF) << 4);
+      o[(2 * g + 1) * 16 + i] = (a >> 4) | ((c >> 4) << 4);
+    }
+  }
+}
+
+int launch_gguf_q8(const uint8_t* raw, long long blocks, void* d, int8_t* qs, cudaStream_t st) {
+  if (blocks == 0) return B200MOE_OK;
+  const long long n = blocks * 32;
+  gguf_q8_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
+      raw, blocks, static_cast<uint16_t*>(d), qs);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int launch_gguf_q4k(const uint8_t* raw, long long blocks, void* d, void* dmin, uint8_t* sh,
+                    uint8_t* sl, uint8_t* mh, uint8_t* ml, uint8_t* qs, cudaStream_t st) {
+  if (blocks == 0) return B200MOE_OK;
+  gguf_q4k_kernel<<<static_cast<unsigned>((blocks + 127) / 128), 128, 0, st>>>(
+      raw, blocks, static_cast<uint16_t*>(d), static_cast<uint16_t*>(dmin), sh, sl, mh, ml, qs);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+}  // namespace b200moe

@@ -1,0 +1,547 @@
+// Weight-streaming grouped expert GEMM for the decode regime (few tokens per
+// expert, HBM-bound).
+//
+// Orientation is "swap-AB": a 16x16 tile of *weights* is the A operand of
+// mma.sync.m16n8k16 and 8 tokens form the N dimension, so an expert with 1..8
+// tokens costs one MMA column block and the quantised weights are read from HBM
+// exactly once.  A producer warp streams the quantised weight tiles, their
+// block scales and the tokens' activation rows into a shared-memory ring with
+// TMA (128-byte swizzle); eight consumer warps dequantise straight from the
+// staged bytes into MMA fragments in registers (no shared-memory round trip
+// for the dequantised values) and accumulate in fp32.
+//
+// One CTA per SM, persistent over work items (expert, row tile, k split, token
+// chunk).  Per stage a CTA holds two "row sets" of 64 weight rows x 256 k:
+// gate rows and up rows of the same output columns (fused SiLU/GELU-gated
+// product in the epilogue), or 128 consecutive rows of the down matrix.
+// Consumer warp (w, kh): rows 16w..16w+15 of both sets, k half kh of the
+// stage; the two k halves are added through shared memory at the end of an item.
+#include "common.cuh"
+
+namespace b200moe {
+
+namespace {
+
+constexpr int CONSUMER_WARPS = 8;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int KT = 256;   // reduction elements per stage
+constexpr int SET_ROWS = 64;
+constexpr int MAX_E = 64;
+
+struct StreamArgs {
+  const int32_t* seg;
+  int E, N, K;
+  int ntiles;           // row tiles per expert
+  int ksplit;           // k partitions per row tile
+  int stages_per_item;  // (K / KT) / ksplit
+  int P;                // rows of the activation / output arrays
+  int act;
+  int out_kperm;        // gate/up only: permute output columns for a Q4_K down matrix
+  void* out;
+  int32_t* status;
+};
+
+template <int LAYOUT, int S>
+struct Cfg {
+  static constexpr int MT = 8 * S;  // tokens per chunk
+  // bytes of one row set of quantised values per stage
+  static constexpr int WSET = LAYOUT == B200MOE_LAYOUT_Q8_0   ? SET_ROWS * KT
+                              : LAYOUT == B200MOE_LAYOUT_Q4_K ? SET_ROWS * KT / 2
+                                                              : SET_ROWS * KT * 2;
+  // scale bytes per row per stage
+  static constexpr int SROW = LAYOUT == B200MOE_LAYOUT_Q8_0 ? 16 : LAYOUT == B200MOE_LAYOUT_Q4_K ? 32 : 0;
+  static constexpr int SSET = SET_ROWS * SROW;
+  static constexpr int XBOX = MT * 128;
+  static constexpr int OFF_X = 2 * WSET;
+  static constexpr int OFF_S = OFF_X + 4 * XBOX;
+  static constexpr int STAGE = OFF_S + 2 * SSET;
+  static constexpr int RED_FLOATS = 8 * S < 32 ? 8 * S : 32;  // floats per thread per reduce round
+  static constexpr int RED_BYTES = 128 * RED_FLOATS * 4;
+  static constexpr int BUDGET = 232448 - 1024 - RED_BYTES - 256;
+  static constexpr int STAGES_RAW = BUDGET / STAGE;
+  static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+  static constexpr int SMEM = 1024 + STAGES * STAGE + RED_BYTES + 256;
+  static_assert(STAGE % 1024 == 0, "stage must keep 1024-byte alignment for the swizzle");
+  static_assert(STAGES >= 2, "pipeline too shallow");
+};
+
+__device__ __forceinline__ int rho(int g) { return (g >> 1) | ((g & 1) << 2); }
+
+// half2 with both halves = half `sel` (0 = low, 1 = high) of `v`
+__device__ __forceinline__ __half2 bcast_half(uint32_t v, int sel) {
+  return u32_as_h2(__byte_perm(v, v, sel ? 0x3232 : 0x1010));
+}
+
+// Eight 4-bit quants of one 32-bit word (k order: nibble i of byte b is
+// element 2b+i) -> fp16(fp16(ds*q) - dm) as four half2 whose element pairs are
+// (q0,q4) (q1,q5) (q2,q6) (q3,q7): the pair order the activation rows are
+// pre-permuted to.  0x6400|q is 1024+q exactly, so one subtraction gives q.
+__device__ __forceinline__ void dequant_q4x8(uint32_t w, __half2 ds, __half2 dm,
+                                             uint32_t (&out)[4]) {
+  const __half2 k1024 = u32_as_h2(0x64006400u);
+  const uint32_t w1 = w >> 8;
+  uint32_t e[4];
+  e[0] = (w & 0x000f000fu) | 0x64006400u;          // (q0, q4)
+  e[1] = ((w >> 4) & 0x000f000fu) | 0x64006400u;   // (q1, q5)
+  e[2] = (w1 & 0x000f000fu) | 0x64006400u;         // (q2, q6)
+  e[3] = ((w1 >> 4) & 0x000f000fu) | 0x64006400u;  // (q3, q7)
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 q = __hsub2(u32_as_h2(e[i]), k1024);
+    out[i] = h2_as_u32(__hsub2(__hmul2(ds, q), dm));
+  }
+}
+
+template <int LAYOUT, int NMAT, int S>
+__global__ void __launch_bounds__(THREADS, 1)
+stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
+                   const __grid_constant__ CUtensorMap tm_s0, const __grid_constant__ CUtensorMap tm_s1,
+                   const __grid_constant__ CUtensorMap tm_x, const StreamArgs args) {
+  using C = Cfg<LAYOUT, S>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_seg[MAX_E + 1];
+  __shared__ int s_prefix[MAX_E + 1];
+  __shared__ int s_abort;
+  __shared__ int s_exit;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t red_base = smem_base + STAGES * C::STAGE;
+  const uint32_t bar_base = red_base + C::RED_BYTES;  // full[STAGES], empty[STAGES]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    s_abort = 0;
+    s_exit = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), CONSUMER_WARPS);
+    }
+    fence_mbar_init();
+    int run = 0;
+    for (int e = 0; e < args.E; ++e) {
+      const int a = args.seg[e], b = args.seg[e + 1];
+      s_seg[e] = a;
+      s_prefix[e] = run;
+      const int chunks = (b - a + C::MT - 1) / C::MT;
+      run += chunks * args.ntiles * args.ksplit;
+    }
+    s_seg[args.E] = args.seg[args.E];
+    s_prefix[args.E] = run;
+  }
+  __syncthreads();
+  const int total_items = s_prefix[args.E];
+  volatile int* abort_flag = &s_abort;
+
+  auto decode = [&](int item, int& e, int& tile, int& kc, int& row0, int& rows) {
+    e = 0;
+    while (item >= s_prefix[e + 1]) ++e;
+    const int local = item - s_prefix[e];
+    const int m = s_seg[e + 1] - s_seg[e];
+    const int chunks = (m + C::MT - 1) / C::MT;
+    const int tc = local % chunks;
+    const int rest = local / chunks;
+    kc = rest % args.ksplit;
+    tile = rest / args.ksplit;
+    row0 = s_seg[e] + tc * C::MT;
+    rows = min(C::MT, s_seg[e + 1] - row0);
+  };
+
+  if (warp == CONSUMER_WARPS) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t n = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int e, tile, kc, row0, rows;
+        decode(item, e, tile, kc, row0, rows);
+        const int n0 = tile * (NMAT == 2 ? SET_ROWS : 2 * SET_ROWS);
+        for (int st = 0; st < args.stages_per_item; ++st, ++n) {
+          const int slot = n % STAGES;
+          const uint32_t phase = (n / STAGES) & 1u;
+          if (!mbar_wait(empty_bar(slot), phase ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          const uint32_t sb = smem_base + slot * C::STAGE;
+          const uint32_t fb = full_bar(slot);
+          mbar_expect_tx(fb, C::STAGE);
+          const int k0 = (kc * args.stages_per_item + st) * KT;
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const CUtensorMap* tw = (NMAT == 2 && r == 1) ? &tm_w1 : &tm_w0;
+            const CUtensorMap* ts = (NMAT == 2 && r == 1) ? &tm_s1 : &tm_s0;
+            const int grow = e * args.N + n0 + (NMAT == 2 ? 0 : SET_ROWS * r);
+            if constexpr (LAYOUT == B200MOE_LAYOUT_Q8_0) {
+              tma_load_2d(sb + r * C::WSET, tw, k0, grow, fb);
+              tma_load_2d(sb + r * C::WSET + SET_ROWS * 128, tw, k0 + 128, grow, fb);
+              tma_load_2d(sb + C::OFF_S + r * C::SSET, ts, (k0 / 32) * 2, grow, fb);
+            } else if constexpr (LAYOUT == B200MOE_LAYOUT_Q4_K) {
+              tma_load_2d(sb + r * C::WSET, tw, k0 / 2, grow, fb);
+              tma_load_2d(sb + C::OFF_S + r * C::SSET, ts, (k0 / 32) * 4, grow, fb);
+            } else {
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                tma_load_2d(sb + r * C::WSET + c * (SET_ROWS * 128), tw, (k0 + 64 * c) * 2, grow, fb);
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            tma_load_2d(sb + C::OFF_X + c * C::XBOX, &tm_x, (k0 + 64 * c) * 2, row0, fb);
+        }
+      }
+      // Do not leave while copies may still land in this CTA's shared memory.
+      const uint32_t issued = n;
+      const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
+      for (uint32_t i = first; i < issued; ++i)
+        mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1u, abort_flag, args.status);
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int w = warp & 3, kh = warp >> 2;
+  const int g = lane >> 2, t = lane & 3;
+  const int rg = rho(g);
+  const int ctid = tid & 127;  // index within a k-half group
+  uint32_t n = 0;
+
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    int e, tile, kc, row0, rows;
+    decode(item, e, tile, kc, row0, rows);
+    const int s_act = (rows + 7) >> 3;
+    float acc[2][S][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][s][c] = 0.f;
+
+    for (int st = 0; st < args.stages_per_item; ++st, ++n) {
+      const int slot = n % STAGES;
+      const uint32_t phase = (n / STAGES) & 1u;
+      if (!mbar_wait(full_bar(slot), phase, abort_flag, args.status)) break;
+      const uint32_t sb = smem_base + slot * C::STAGE;
+
+      if constexpr (LAYOUT == B200MOE_LAYOUT_Q8_0) {
+        uint32_t sc[2][2][4];  // [set][row half][8 block scales of the stage]
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const uint32_t srow = sb + C::OFF_S + r * C::SSET + (16 * w + rg) * 16;
+          lds128(srow, sc[r][0]);
+          lds128(srow + 8 * 16, sc[r][1]);
+        }
+#pragma unroll
+        for (int spi = 0; spi < 2; ++spi) {
+          const int sp = 2 * kh + spi;  // 64-k span of the stage
+          const int cb = (sp & 1) * 4;
+          uint32_t alo[2][2][4], ahi[2][2][4];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const uint32_t wbase = sb + r * C::WSET + (sp >> 1) * (SET_ROWS * 128) +
+                                   (16 * w + rg) * 128 + (((cb + t) ^ rg) << 4);
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              uint32_t q[4];
+              lds128(wbase + hf * 8 * 128, q);
+              const uint32_t sw = kh ? sc[r][hf][2 + spi] : sc[r][hf][spi];
+              const __half2 scale = bcast_half(sw, t >> 1);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) dequant_q8x4(q[j], scale, alo[r][hf][j], ahi[r][hf][j]);
+            }
+          }
+#pragma unroll
+          for (int s = 0; s < S; ++s) {
+            if (s < s_act) {
+              const uint32_t xrow = sb + C::OFF_X + sp * C::XBOX + (8 * s + g) * 128;
+              uint32_t b[8];
+              lds128(xrow + (((2 * t) ^ g) << 4), *reinterpret_cast<uint32_t(*)[4]>(&b[0]));
+              lds128(xrow + (((2 * t + 1) ^ g) << 4), *reinterpret_cast<uint32_t(*)[4]>(&b[4]));
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int r = 0; r < 2; ++r)
+                  mma_16816(acc[r][s], alo[r][0][j], alo[r][1][j], ahi[r][0][j], ahi[r][1][j],
+                            b[2 * j], b[2 * j + 1]);
+            }
+          }
+        }
+      } else if constexpr (LAYOUT == B200MOE_LAYOUT_F16) {
+        // dense fp16 weights: one 128-byte box per 64-k span, fragments are the
+        // staged values themselves
+#pragma unroll
+        for (int spi = 0; spi < 2; ++spi) {
+          const int sp = 2 * kh + spi;
+          uint32_t a[2][2][8];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              const uint32_t wrow = sb + r * C::WSET + sp * (SET_ROWS * 128) +
+                                    (16 * w + rg + 8 * hf) * 128;
+              lds128(wrow + (((2 * t) ^ rg) << 4), *reinterpret_cast<uint32_t(*)[4]>(&a[r][hf][0]));
+              lds128(wrow + (((2 * t + 1) ^ rg) << 4), *reinterpret_cast<uint32_t(*)[4]>(&a[r][hf][4]));
+            }
+          }
+#pragma unroll
+          for (int s = 0; s < S; ++s) {
+            if (s < s_act) {
+              const uint32_t xrow = sb + C::OFF_X + sp * C::XBOX + (8 * s + g) * 128;
+              uint32_t b[8];
+              lds128(xrow + (((2 * t) ^ g) << 4), *reinterpret_cast<uint32_t(*)[4]>(&b[0]));
+              lds128(xrow + (((2 * t + 1) ^ g) << 4), *reinterpret_cast<uint32_t(*)[4]>(&b[4]));
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int r = 0; r < 2; ++r)
+                  mma_16816(acc[r][s], a[r][0][2 * j], a[r][1][2 * j], a[r][0][2 * j + 1],
+                            a[r][1][2 * j + 1], b[2 * j], b[2 * j + 1]);
+            }
+          }
+        }
+      } else {
+        // Q4_K: one 128-byte box row = 256 k = one super-block; a 64-k span is
+        // 32 bytes; thread t owns 8 bytes = 16 quants of sub-block 2*sp + (t>>1).
+#pragma unroll
+        for (int spi = 0; spi < 2; ++spi) {
+          const int sp = 2 * kh + spi;
+          uint32_t a[2][2][4][2];  // [set][row half][mma j][lo,hi]
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              const int row = 16 * w + rg + 8 * hf;
+              // bytes sp*32 + t*8 .. +8 of the row: chunk 2*sp + (t>>1), half (t&1)
+              const uint32_t addr = sb + r * C::WSET + row * 128 +
+                                    (((2 * sp + (t >> 1)) ^ rg) << 4) + 8 * (t & 1);
+              uint32_t q[2];
+              lds64(addr, q);
+              const uint32_t sm =
+                  lds32(sb + C::OFF_S + r * C::SSET + row * 32 + (2 * sp + (t >> 1)) * 4);
+              const __half2 ds = bcast_half(sm, 0), dm = bcast_half(sm, 1);
+              uint32_t o0[4], o1[4];
+              dequant_q4x8(q[0], ds, dm, o0);
+              dequant_q4x8(q[1], ds, dm, o1);
+              // word q[0] covers k 0..7 of the thread's 16, q[1] covers 8..15;
+              // mma j uses the thread's k 4j..4j+3 in permuted order, i.e. the
+              // pairs (2 per half-word) numbered 2j and 2j+1 of the 8 produced.
+              a[r][hf][0][0] = o0[0]; a[r][hf][0][1] = o0[1];
+              a[r][hf][1][0] = o0[2]; a[r][hf][1][1] = o0[3];
+              a[r][hf][2][0] = o1[0]; a[r][hf][2][1] = o1[1];
+              a[r][hf][3][0] = o1[2]; a[r][hf][3][1] = o1[3];
+            }
+          }
+#pragma unroll
+          for (int s = 0; s < S; ++s) {
+            if (s < s_act) {
+              const uint32_t xrow = sb + C::OFF_X + sp * C::XBOX + (8 * s + g) * 128;
+              uint32_t b[8];
+              lds128(xrow + (((2 * t) ^ g) << 4), *reinterpret_cast<uint32_t(*)[4]>(&b[0]));
+              lds128(xrow + (((2 * t + 1) ^ g) << 4), *reinterpret_cast<uint32_t(*)[4]>(&b[4]));
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int r = 0; r < 2; ++r)
+                  mma_16816(acc[r][s], a[r][0][j][0], a[r][1][j][0], a[r][0][j][1], a[r][1][j][1],
+                            b[2 * j], b[2 * j + 1]);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(slot));
+    }
+
+    // ---- add the two k halves: kh=1 warps hand their sums to kh=0 warps
+    constexpr int TOTAL = 8 * S;
+    constexpr int ROUNDS = TOTAL / C::RED_FLOATS;
+    float* accf = &acc[0][0][0];
+    float* red = reinterpret_cast<float*>(smem_raw + (red_base - smem_u32(smem_raw)));
+#pragma unroll
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+      if (kh == 1) {
+#pragma unroll
+        for (int i = 0; i < C::RED_FLOATS; ++i) red[i * 128 + ctid] = accf[rd * C::RED_FLOATS + i];
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (kh == 0) {
+#pragma unroll
+        for (int i = 0; i < C::RED_FLOATS; ++i) accf[rd * C::RED_FLOATS + i] += red[i * 128 + ctid];
+        // one thread decides for all consumers whether the CTA gives up, so
+        // that every warp leaves the item loop at the same barrier
+        if (rd == ROUNDS - 1 && ctid == 0) s_exit = *abort_flag;
+      }
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+    }
+    if (s_exit) break;
+    if (kh != 0) continue;
+
+    // ---- epilogue
+    const int seg_end = row0 + rows;
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      if (s >= s_act) continue;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int tok = row0 + 8 * s + 2 * t + (c & 1);
+        if (tok >= seg_end) continue;
+        const int rsub = 16 * w + rg + 8 * (c >> 1);
+        if constexpr (NMAT == 2) {
+          const float gt = acc[0][s][c], up = acc[1][s][c];
+          const float a = args.act == B200MOE_ACT_SILU ? silu_f(gt) : gelu_erf_f(gt);
+          int col = tile * SET_ROWS + rsub;
+          if (args.out_kperm) col = (col & ~7) | ((col & 3) << 1) | ((col >> 2) & 1);
+          static_cast<__half*>(args.out)[static_cast<size_t>(tok) * args.N + col] =
+              to_half_sat(a * up);
+        } else {
+          float* outp = static_cast<float*>(args.out) +
+                        static_cast<size_t>(kc) * args.P * args.N +
+                        static_cast<size_t>(tok) * args.N + tile * (2 * SET_ROWS) + rsub;
+          outp[0] = acc[0][s][c];
+          outp[SET_ROWS] = acc[1][s][c];
+        }
+      }
+    }
+  }
+}
+
+template <int LAYOUT, int NMAT, int S>
+int launch_t(const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
+  using C = Cfg<LAYOUT, S>;
+  auto kern = stream_gemm_kernel<LAYOUT, NMAT, S>;
+  static bool configured[16] = {};
+  int dev = 0;
+  B200_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 16 && !configured[dev]) {
+    B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    configured[dev] = true;
+  }
+  kern<<<sm_count(), THREADS, C::SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], a);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+template <int LAYOUT, int NMAT>
+int launch_s(int S, const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
+  switch (S) {
+    case 1: return launch_t<LAYOUT, NMAT, 1>(maps, a, st);
+    case 2: return launch_t<LAYOUT, NMAT, 2>(maps, a, st);
+    case 4: return launch_t<LAYOUT, NMAT, 4>(maps, a, st);
+    default: return launch_t<LAYOUT, NMAT, 8>(maps, a, st);
+  }
+}
+
+int weight_maps(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts) {
+  const uint64_t rows = static_cast<uint64_t>(w->experts) * w->rows;
+  if (w->layout == B200MOE_LAYOUT_Q8_0) {
+    if (int rc = make_tmap_2d(tw, w->qs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, w->cols, SET_ROWS,
+                              128, true))
+      return rc;
+    return make_tmap_2d(ts, w->d, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, w->cols / 32 * 2,
+                        SET_ROWS, 16, false);
+  }
+  if (w->layout == B200MOE_LAYOUT_F16) {
+    *ts = CUtensorMap{};
+    return make_tmap_2d(tw, w->qs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows,
+                        static_cast<uint64_t>(w->cols) * 2, SET_ROWS, 128, true);
+  }
+  if (int rc = make_tmap_2d(tw, w->qs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, w->cols / 2,
+                            SET_ROWS, 128, true))
+    return rc;
+  return make_tmap_2d(ts, w->sub, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, w->cols / 32 * 4,
+                      SET_ROWS, 32, false);
+}
+
+int pick_s(int max_segment) {
+  if (max_segment <= 8) return 1;
+  if (max_segment <= 16) return 2;
+  if (max_segment <= 32) return 4;
+  return 8;
+}
+
+int check_weight(const b200moe_weight_t* w, const char* name) {
+  B200_REQUIRE(w->layout == B200MOE_LAYOUT_Q8_0 || w->layout == B200MOE_LAYOUT_Q4_K ||
+                   w->layout == B200MOE_LAYOUT_F16,
+               "stream kernel: %s layout %d unsupported", name, w->layout);
+  B200_REQUIRE(w->cols % KT == 0, "stream kernel: %s cols (%d) must be a multiple of 256", name,
+               w->cols);
+  B200_REQUIRE(w->experts >= 1 && w->experts <= MAX_E, "stream kernel: %s experts out of range",
+               name);
+  B200_REQUIRE(w->qs != nullptr, "stream kernel: %s has no data", name);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(w->qs) & 15) == 0, "stream kernel: %s qs misaligned",
+               name);
+  if (w->layout == B200MOE_LAYOUT_Q8_0)
+    B200_REQUIRE(w->d != nullptr && (reinterpret_cast<uintptr_t>(w->d) & 15) == 0,
+                 "stream kernel: %s scales missing or misaligned", name);
+  else if (w->layout == B200MOE_LAYOUT_Q4_K)
+    B200_REQUIRE(w->sub != nullptr && (reinterpret_cast<uintptr_t>(w->sub) & 15) == 0,
+                 "stream kernel: %s sub-block scales missing or misaligned", name);
+  return B200MOE_OK;
+}
+
+}  // namespace
+
+int stream_down_ksplit(const b200moe_weight_t* down, int pairs) {
+  const int stages = down->cols / KT;
+  if (pairs > 1024) return 1;
+  if (stages % 4 == 0 && stages >= 8) return 4;
+  if (stages % 2 == 0 && stages >= 4) return 2;
+  return 1;
+}
+
+int launch_stream_gate_up(const void* xs, const int32_t* seg, int pairs, int max_segment,
+                          const b200moe_weight_t* gate, const b200moe_weight_t* up, int act,
+                          int out_kperm, void* a_out, cudaStream_t st) {
+  if (int rc = check_weight(gate, "gate")) return rc;
+  if (int rc = check_weight(up, "up")) return rc;
+  B200_REQUIRE(gate->layout == up->layout && gate->rows == up->rows && gate->cols == up->cols &&
+                   gate->experts == up->experts,
+               "stream kernel: gate and up must have the same layout and shape");
+  B200_REQUIRE(gate->rows % SET_ROWS == 0, "stream kernel: ffn (%d) must be a multiple of 64",
+               gate->rows);
+  if (pairs == 0) return B200MOE_OK;
+  const int S = pick_s(max_segment);
+  CUtensorMap maps[5];
+  if (int rc = weight_maps(gate, &maps[0], &maps[2])) return rc;
+  if (int rc = weight_maps(up, &maps[1], &maps[3])) return rc;
+  if (int rc = make_tmap_2d(&maps[4], xs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pairs,
+                            static_cast<uint64_t>(gate->cols) * 2, 8 * S, 128, true))
+    return rc;
+  StreamArgs a{};
+  a.seg = seg; a.E = gate->experts; a.N = gate->rows; a.K = gate->cols;
+  a.ntiles = gate->rows / SET_ROWS; a.ksplit = 1; a.stages_per_item = gate->cols / KT;
+  a.P = pairs; a.act = act; a.out_kperm = out_kperm; a.out = a_out; a.status = device_status_ptr();
+  if (a.status == nullptr) return B200MOE_ERR_CUDA;
+  if (gate->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 2>(S, maps, a, st);
+  if (gate->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 2>(S, maps, a, st);
+  return launch_s<B200MOE_LAYOUT_Q4_K, 2>(S, maps, a, st);
+}
+
+int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_segment,
+                       const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st) {
+  if (int rc = check_weight(down, "down")) return rc;
+  B200_REQUIRE(down->rows % (2 * SET_ROWS) == 0,
+               "stream kernel: hidden (%d) must be a multiple of 128", down->rows);
+  B200_REQUIRE(ksplit >= 1 && (down->cols / KT) % ksplit == 0, "stream kernel: bad k split %d",
+               ksplit);
+  if (pairs == 0) return B200MOE_OK;
+  const int S = pick_s(max_segment);
+  CUtensorMap maps[5];
+  if (int rc = weight_maps(down, &maps[0], &maps[2])) return rc;
+  maps[1] = maps[0];
+  maps[3] = maps[2];
+  if (int rc = make_tmap_2d(&maps[4], a_in, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pairs,
+                            static_cast<uint64_t>(down->cols) * 2, 8 * S, 128, true))
+    return rc;
+  StreamArgs a{};
+  a.seg = seg; a.E = down->experts; a.N = down->rows; a.K = down->cols;
+  a.ntiles = down->rows / (2 * SET_ROWS); a.ksplit = ksplit;
+  a.stages_per_item = down->cols / KT / ksplit;
+  a.P = pairs; a.act = 0; a.out_kperm = 0; a.out = d_out; a.status = device_status_ptr();
+  if (a.status == nullptr) return B200MOE_ERR_CUDA;
+  if (down->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 1>(S, maps, a, st);
+  if (down->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 1>(S, maps, a, st);
+  return launch_s<B200MOE_LAYOUT_Q4_K, 1>(S, maps, a, st);
+}
+
+}  // namespace b200moe

@@ -1,0 +1,423 @@
+"""Host side of the MoE FFN path: weight preparation, the staged calls into the
+C ABI, the fused `B200MoeBlock`, and the op-level overrides.
+
+Two ways in, mirroring how the reference layer is written:
+
+* `B200MoeBlock(theta, expert_count, expert_used_count, rms_epsilon,
+  moe_activation)` has the constructor and `forward(h)` of sharktank's
+  `MoeBlock` (layers/mixture_of_experts_block.py:23-90) and runs the whole layer
+  as one library call.
+* `get_index` / `einsum_2args` overrides make sharktank's own
+  `PreGatherFFNMOE.forward` (layers/ffn_moe_block.py:60-74) work on quantized
+  expert tensors: `weights[experts, :, :]` returns a lazy `GatheredExperts`
+  handle instead of a dense copy, and the three MoE einsums run as grouped
+  products over the permuted tokens.
+
+Everything computes on the GPU through libb200moe; tensors on the CPU are
+declined (`NotImplemented`) or rejected, never evaluated.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Any, Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _cabi as C
+from . import ops as _ops
+
+_DT = {torch.float32: C.DT_F32, torch.float16: C.DT_F16, torch.bfloat16: C.DT_BF16}
+REGIMES = {"auto": C.REGIME_AUTO, "stream": C.REGIME_STREAM, "tensor": C.REGIME_TENSOR}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(t: torch.Tensor, what: str):
+    if not t.is_cuda:
+        raise C.B200MoeError(f"{what} must be a CUDA tensor (there is no CPU path)")
+
+
+def device_status() -> int:
+    """Reads and clears the device status word; raises if a kernel reported an
+    error (bounded wait timed out, bounds check failed)."""
+    st = ctypes.c_int32(0)
+    C.check(C.lib.b200moe_device_status(_stream(), ctypes.byref(st)), "device_status")
+    return st.value
+
+
+# ---------------------------------------------------------------- weights
+@dataclass
+class PreparedWeight:
+    """Device buffers of one stacked expert tensor plus its C descriptor."""
+
+    desc: C.WeightDesc
+    layout: int
+    experts: int
+    rows: int
+    cols: int
+    keep: tuple  # tensors the descriptor points into
+
+    @property
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.keep)
+
+
+def _layout_name(t) -> Optional[str]:
+    lt = getattr(t, "layout_type", None)
+    return getattr(lt, "__name__", None)
+
+
+def _unbox(t) -> torch.Tensor:
+    if isinstance(t, torch.Tensor):
+        return t
+    if hasattr(t, "as_torch"):
+        return t.as_torch()
+    raise TypeError(f"expected a tensor, got {type(t).__name__}")
+
+
+def prepare_weight(t: Any) -> PreparedWeight:
+    """Turns `ffn_*_exps.weight` (a PlanarQuantizedTensor with a Q8_0 /
+    Q4_K planar layout — sharktank's or this package's — or a dense tensor) into
+    the descriptor the kernels take.  Q8_0 planes are used in place; Q4_K gets
+    one derived array (per-sub-block scale/min pairs).  The result is cached on
+    the tensor object."""
+    cached = getattr(t, "_b200moe_prepared", None)
+    if cached is not None:
+        return cached
+    name = _layout_name(t)
+    if name is None:
+        w = _unbox(t)
+        _require_cuda(w, "expert weight")
+        assert w.dim() == 3, "expert weights are [experts, rows, cols]"
+        w16 = w.to(torch.float16).contiguous()
+        e, n, k = w16.shape
+        desc = C.WeightDesc(C.LAYOUT_F16, e, n, k, w16.data_ptr(), None, None)
+        prep = PreparedWeight(desc, C.LAYOUT_F16, e, n, k, (w16,))
+    else:
+        e, n, k = (int(v) for v in t.shape)
+        planes = t.unpack().planes
+        for p in planes.values():
+            _require_cuda(p, "expert weight plane")
+        if name == "BlockScaledLayout":
+            if "m" in planes:
+                raise C.B200MoeError("BlockScaledLayout with offsets is not supported")
+            qs = planes["qs"].contiguous().view(torch.int8)
+            d = planes["d"].contiguous()
+            assert d.dtype == torch.float16 and qs.numel() == e * n * k and d.numel() == e * n * k // 32
+            desc = C.WeightDesc(C.LAYOUT_Q8_0, e, n, k, qs.data_ptr(), d.data_ptr(), None)
+            prep = PreparedWeight(desc, C.LAYOUT_Q8_0, e, n, k, (qs, d))
+        elif name == "SuperBlockOffsetScaled_4_6_Layout":
+            qs = planes["qs"].contiguous().view(torch.uint8)
+            assert qs.numel() == e * n * k // 2
+            blocks = e * n * k // 256
+            sub = torch.empty(blocks * 8, 2, dtype=torch.float16, device=qs.device)
+            args = [planes[nm].contiguous() for nm in
+                    ("d", "dmin", "sb_scales_high", "sb_scales_low", "sb_mins_high", "sb_mins_low")]
+            with torch.cuda.device(qs.device):
+                C.check(C.lib.b200moe_q4k_prepare(*[_ptr(a) for a in args], blocks, _ptr(sub),
+                                                  _stream()), "q4k_prepare")
+            desc = C.WeightDesc(C.LAYOUT_Q4_K, e, n, k, qs.data_ptr(), None, sub.data_ptr())
+            prep = PreparedWeight(desc, C.LAYOUT_Q4_K, e, n, k, (qs, sub))
+        else:
+            raise C.B200MoeError(f"unsupported quantized layout {name}")
+    try:
+        t._b200moe_prepared = prep
+    except AttributeError:
+        pass
+    return prep
+
+
+def dequant_layout(layout, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """`layout.dequant(dtype)` on the GPU, bit-exact with the reference
+    (types/layouts.py:274-290 and :505-517)."""
+
+    class _Holder:
+        pass
+
+    h = _Holder()
+    h.layout_type = type(layout)
+    h.shape = list(layout.shape)
+    h.unpack = lambda: layout
+    shape = list(layout.shape)
+    if len(shape) == 2:
+        h.shape = [1] + shape
+    elif len(shape) != 3:
+        lead = 1
+        for v in shape[:-2]:
+            lead *= int(v)
+        h.shape = [lead] + shape[-2:]
+    prep = prepare_weight(h)
+    is_q4k = prep.layout == C.LAYOUT_Q4_K
+    out_dtype = torch.float16 if (dtype is None or is_q4k) else dtype
+    if out_dtype not in (torch.float16, torch.float32):
+        raise C.B200MoeError(f"dequant to {out_dtype} is not supported")
+    dev = prep.keep[0].device
+    out = torch.empty(shape, dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        C.check(C.lib.b200moe_dequant(ctypes.byref(prep.desc), _DT[out_dtype], _ptr(out), _stream()),
+                "dequant")
+    return out
+
+
+# ------------------------------------------------------------ staged calls
+@dataclass
+class RoutePlan:
+    counts: torch.Tensor       # int32 [E_local]
+    seg_offsets: torch.Tensor  # int32 [E_local + 1]
+    perm: torch.Tensor         # int32 [pairs]: sorted position -> pair
+    inv: torch.Tensor          # int32 [pairs]: pair -> sorted position (or -1)
+    pairs: int
+    top_k: int
+
+
+def route_plan(experts: torch.Tensor, expert_count: int, expert_begin: int = 0) -> RoutePlan:
+    """Stable grouping of (token, slot) pairs by expert id on the GPU."""
+    _require_cuda(experts, "experts")
+    ex = experts.to(torch.int32).contiguous()
+    pairs = ex.numel()
+    top_k = ex.shape[-1] if ex.dim() > 1 else 1
+    dev = ex.device
+    counts = torch.empty(expert_count, dtype=torch.int32, device=dev)
+    seg = torch.empty(expert_count + 1, dtype=torch.int32, device=dev)
+    perm = torch.empty(max(pairs, 1), dtype=torch.int32, device=dev)
+    inv = torch.empty(max(pairs, 1), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        C.check(C.lib.b200moe_route_plan(_ptr(ex), pairs, expert_begin, expert_count, _ptr(counts),
+                                         _ptr(seg), _ptr(perm), _ptr(inv), _stream()), "route_plan")
+    return RoutePlan(counts, seg, perm[:pairs], inv[:pairs], pairs, top_k)
+
+
+def grouped_matmul(xs: torch.Tensor, plan_seg: torch.Tensor, w: PreparedWeight, max_segment: int,
+                   regime: int = C.REGIME_AUTO) -> torch.Tensor:
+    """out[p,:] = W[e(p)] @ xs[p,:] for rows p sorted by expert (fp16 in, fp32 out)."""
+    pairs = xs.shape[0]
+    dev = xs.device
+    ks = C.lib.b200moe_down_ksplit(ctypes.byref(w.desc), pairs, max_segment, regime)
+    part = torch.empty(ks, max(pairs, 1), w.rows, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        C.check(C.lib.b200moe_down(_ptr(xs), _ptr(plan_seg), pairs, max_segment,
+                                   ctypes.byref(w.desc), regime, _ptr(part), _stream()), "down")
+    out = part[0] if ks == 1 else part.sum(dim=0)
+    return out[:pairs]
+
+
+# -------------------------------------------------------------- the layer
+class PreparedLayer:
+    """All device-side state of one MoE layer: descriptor, weights, workspace."""
+
+    def __init__(self, theta, expert_count: int, expert_used_count: int, rms_epsilon: float,
+                 activation: str):
+        self.gate = prepare_weight(theta.tensor("ffn_gate_exps", "weight"))
+        self.up = prepare_weight(theta.tensor("ffn_up_exps", "weight"))
+        self.down = prepare_weight(theta.tensor("ffn_down_exps", "weight"))
+        dev = self.gate.keep[0].device
+        self.device = dev
+
+        def f32(t):
+            return None if t is None else _unbox(t).to(device=dev, dtype=torch.float32).contiguous()
+
+        self.norm_w = f32(theta.tensor("ffn_norm", "weight"))
+        router = theta("ffn_gate_inp")
+        self.router_w = f32(router.tensor("weight"))
+        self.router_b = f32(router.optional_tensor("bias")) if "bias" in router.keys else None
+        self.out_norm_w = None
+        if theta.optional_tensor("layer_output_norm") is not None:
+            self.out_norm_w = f32(theta("layer_output_norm").tensor("weight"))
+        self.expert_count = expert_count
+        self.top_k = expert_used_count
+        self.hidden = self.gate.cols
+        self.ffn = self.gate.rows
+        self.desc = C.LayerDesc(
+            self.hidden, self.ffn, expert_count, expert_used_count,
+            C.ACT_SILU if activation == "silu" else C.ACT_GELU, float(rms_epsilon),
+            self.norm_w.data_ptr(), self.router_w.data_ptr(),
+            None if self.router_b is None else self.router_b.data_ptr(),
+            None if self.out_norm_w is None else self.out_norm_w.data_ptr(),
+            self.gate.desc, self.up.desc, self.down.desc, 0,
+        )
+        self._workspace: Optional[torch.Tensor] = None
+        self._workspace_tokens = 0
+
+    def workspace(self, tokens: int) -> torch.Tensor:
+        if self._workspace is None or tokens > self._workspace_tokens:
+            nbytes = C.lib.b200moe_workspace_bytes(ctypes.byref(self.desc), tokens)
+            self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self._workspace_tokens = tokens
+        return self._workspace
+
+    def forward(self, h: torch.Tensor, regime: int = C.REGIME_AUTO, want_routing: bool = False):
+        _require_cuda(h, "h")
+        if h.dtype not in (torch.float32, torch.bfloat16):
+            raise C.B200MoeError(f"activations must be fp32 or bf16, got {h.dtype}")
+        shape = h.shape
+        x = h.reshape(-1, shape[-1]).contiguous()
+        tokens = x.shape[0]
+        y = torch.empty_like(x)
+        experts = gates = None
+        if want_routing:
+            experts = torch.empty(tokens, self.top_k, dtype=torch.int32, device=x.device)
+            gates = torch.empty(tokens, self.top_k, dtype=torch.float32, device=x.device)
+        ws = self.workspace(tokens)
+        with torch.cuda.device(self.device):
+            C.check(C.lib.b200moe_layer_forward(
+                ctypes.byref(self.desc), _ptr(x), _ptr(y), _DT[x.dtype], tokens, regime, _ptr(ws),
+                ws.numel(), _ptr(experts), _ptr(gates), _stream()), "layer_forward")
+        y = y.reshape(shape)
+        return (y, experts, gates) if want_routing else y
+
+
+_LAYERS: dict[int, PreparedLayer] = {}
+
+
+@torch.library.custom_op("b200moe::layer_forward", mutates_args=())
+def _layer_forward_op(h: torch.Tensor, handle: int, regime: int) -> torch.Tensor:
+    return _LAYERS[handle].forward(h, regime)
+
+
+@_layer_forward_op.register_fake
+def _(h, handle, regime):
+    return torch.empty_like(h)
+
+
+def _activation_name(fn) -> str:
+    if fn in (F.silu, torch.nn.functional.silu) or getattr(fn, "__name__", "") == "silu":
+        return "silu"
+    if fn in (F.gelu, torch.nn.functional.gelu) or getattr(fn, "__name__", "") == "gelu":
+        return "gelu"
+    raise C.B200MoeError(f"unsupported MoE activation {fn!r} (silu and gelu are implemented)")
+
+
+class B200MoeBlock(torch.nn.Module):
+    """Drop-in for sharktank's MoeBlock: same constructor, same theta keys
+    (`ffn_gate_inp`, `ffn_norm`, optional `layer_output_norm`,
+    `ffn_{gate,up,down}_exps.weight`), same `forward(h[bs, sl, d])`."""
+
+    def __init__(self, theta, expert_count: int, expert_used_count: int, rms_epsilon: float,
+                 moe_activation=F.silu, *, regime: str = "auto"):
+        super().__init__()
+        self.theta = theta
+        self.expert_count = expert_count
+        self.expert_used_count = expert_used_count
+        self.layer = PreparedLayer(theta, expert_count, expert_used_count, rms_epsilon,
+                                   _activation_name(moe_activation))
+        self.regime = REGIMES[regime]
+        self._handle = id(self.layer)
+        _LAYERS[self._handle] = self.layer
+
+    def __del__(self):
+        _LAYERS.pop(getattr(self, "_handle", None), None)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return torch.ops.b200moe.layer_forward(h, self._handle, self.regime)
+
+
+# ------------------------------------------------------ op-level overrides
+class GatheredExperts:
+    """What `ffn_*_exps.weight[experts, :, :]` returns for a quantized tensor: a
+    handle on (weights, experts) with the logical shape [T, k, N, K] of the dense
+    gather the reference would have materialised (layers/ffn_moe_block.py:39)."""
+
+    def __init__(self, base, experts: torch.Tensor):
+        self.base = base
+        self.experts = experts
+        t, k = experts.shape
+        self.shape = [t, k, int(base.shape[1]), int(base.shape[2])]
+        self._plan: Optional[RoutePlan] = None
+
+    def plan(self) -> RoutePlan:
+        if self._plan is None:
+            self._plan = _cached_plan(self.experts, int(self.base.shape[0]))
+        return self._plan
+
+
+_PLAN_CACHE: dict = {}
+
+
+def _cached_plan(experts: torch.Tensor, expert_count: int) -> RoutePlan:
+    key = (experts.data_ptr(), experts._version, tuple(experts.shape), expert_count)
+    hit = _PLAN_CACHE.get("key")
+    if hit == key:
+        return _PLAN_CACHE["plan"]
+    plan = route_plan(experts, expert_count)
+    _PLAN_CACHE["key"], _PLAN_CACHE["plan"] = key, plan
+    return plan
+
+
+_SUPPORTED = ("BlockScaledLayout", "SuperBlockOffsetScaled_4_6_Layout")
+
+
+def get_index_quantized(tensor, key):
+    """`get_index` override: `weights[experts, :, :]` on a Q8_0 / Q4_K planar
+    tensor -> lazy GatheredExperts.  Anything else is declined."""
+    if _layout_name(tensor) not in _SUPPORTED:
+        return NotImplemented
+    if not (isinstance(key, tuple) and len(key) == 3 and isinstance(key[0], torch.Tensor)):
+        return NotImplemented
+    idx = key[0]
+    if idx.dtype not in (torch.int64, torch.int32) or idx.dim() != 2 or not idx.is_cuda:
+        return NotImplemented
+    if key[1] != slice(None) or key[2] != slice(None):
+        return NotImplemented
+    return GatheredExperts(tensor, idx)
+
+
+def einsum_2args_gathered(input0, input1, einsum_str):
+    """`einsum_2args` override for the MoE strings with a GatheredExperts rhs
+    (ops/default_impls.py:72-94): "mk,menk->men" and "mek,menk->men"."""
+    if not isinstance(input1, GatheredExperts):
+        return NotImplemented
+    x = _unbox(input0)
+    if not x.is_cuda:
+        return NotImplemented
+    plan = input1.plan()
+    w = prepare_weight(input1.base)
+    t, k = input1.experts.shape
+    kperm = C.lib.b200moe_kperm(w.layout, C.REGIME_AUTO, t)
+    if einsum_str == "mk,menk->men":
+        rows = x.to(torch.float16).contiguous()
+        xs = torch.empty(plan.pairs, w.cols, dtype=torch.float16, device=x.device)
+        with torch.cuda.device(x.device):
+            C.check(C.lib.b200moe_permute_rows(_ptr(rows), _ptr(plan.perm), _ptr(plan.seg_offsets),
+                                               w.experts, plan.pairs, k, w.cols, kperm, _ptr(xs),
+                                               _stream()), "permute_rows")
+    elif einsum_str == "mek,menk->men":
+        rows = x.reshape(t * k, -1).to(torch.float16)
+        xs = rows.index_select(0, plan.perm.to(torch.int64)).contiguous()
+        if kperm:
+            xs = xs.view(plan.pairs, -1, 2, 4).transpose(2, 3).reshape(plan.pairs, -1).contiguous()
+    else:
+        return NotImplemented
+    out = grouped_matmul(xs, plan.seg_offsets, w, t)
+    return out.index_select(0, plan.inv.to(torch.int64)).view(t, k, w.rows).to(x.dtype)
+
+
+def einsum_2args_gate_scale(input0, input1, einsum_str):
+    """"me,men->men" on CUDA tensors: the gate scaling (ops/default_impls.py:97-105)."""
+    if einsum_str != "me,men->men":
+        return NotImplemented
+    a, b = _unbox(input0), _unbox(input1)
+    return a.unsqueeze(-1) * b
+
+
+def register_overrides(ops_module=_ops, quantized_type=None, tensor_type=torch.Tensor, salience=10):
+    """Registers the overrides with an ops registry: this package's mirror by
+    default, sharktank's own when called from `plugin.register`."""
+    from . import types as _types
+
+    qt = quantized_type or _types.QuantizedTensor
+    ops_module.get_index.override(qt, salience=salience)(get_index_quantized)
+    ops_module.einsum_2args.override(tensor_type, GatheredExperts, salience=salience)(
+        einsum_2args_gathered)
+    if ops_module is _ops:
+        ops_module.einsum_2args.override(torch.Tensor, torch.Tensor)(einsum_2args_gate_scale)
+
+
+register_overrides()

@@ -1,0 +1,126 @@
+"""Host-side logic that needs no GPU: the C ABI loads and exports what the
+header declares, the registry mirror follows the reference's dispatch rules,
+the type mirror behaves like sharktank's containers."""
+import os
+import sys
+
+import pytest
+import torch
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built_library():
+    from shark_platform_b200 import build
+
+    build.build()
+
+
+def test_cabi_exports_every_declared_symbol():
+    from shark_platform_b200 import _cabi as C
+
+    names = C.declared_symbols()
+    assert len(names) >= 18
+    for n in names:
+        assert hasattr(C.lib, n), n
+        assert n in C._PROTOS, f"{n} has no ctypes prototype"
+    assert set(C._PROTOS) == set(names)
+    assert b"sm_100a" in C.lib.b200moe_version()
+
+
+def test_registry_salience_order_and_decline():
+    from shark_platform_b200 import ops
+
+    disp = ops.SignatureDispatcher(lambda a, b: None, (0, 1))
+    calls = []
+
+    @disp.override(torch.Tensor, torch.Tensor)
+    def base(a, b):
+        calls.append("base")
+        return "base"
+
+    @disp.override(torch.Tensor, torch.Tensor)
+    def later(a, b):
+        calls.append("later")
+        return NotImplemented
+
+    @disp.override(torch.Tensor, torch.Tensor, salience=5)
+    def salient(a, b):
+        calls.append("salient")
+        return NotImplemented
+
+    x = torch.zeros(1)
+    assert disp(x, x) == "base"
+    assert calls == ["salient", "later", "base"]  # salience first, then latest registered
+    with pytest.raises(NotImplementedError):
+        disp(x, 3)
+
+
+def test_overrides_are_registered_in_the_mirror():
+    from shark_platform_b200 import moe, ops, types as T
+
+    lay = T.BlockScaledLayout([2, 64, 256], torch.zeros(2, 64, 8, 1, dtype=torch.float16),
+                              torch.zeros(2, 64, 8, 32, dtype=torch.int8))
+    q = T.PlanarQuantizedTensor(shape=[2, 64, 256], layout=lay)
+    assert moe.get_index_quantized in list(ops.get_index.find_overrides((q,)))
+    # CPU index tensors are declined, never computed on the host
+    with pytest.raises(NotImplementedError):
+        q[torch.zeros(3, 2, dtype=torch.int64), :, :]
+    g = moe.GatheredExperts(q, torch.zeros(3, 2, dtype=torch.int64))
+    assert g.shape == [3, 2, 64, 256]
+    assert moe.einsum_2args_gathered in list(ops.einsum_2args.find_overrides((torch.zeros(1), g)))
+    with pytest.raises(NotImplementedError):
+        ops.einsum_2args(torch.zeros(3, 256), g, "mk,menk->men")  # CPU activations: declined
+
+
+def test_theta_mirror_matches_reference_accessors():
+    from shark_platform_b200 import types as T
+
+    w = T.DefaultPrimitiveTensor(data=torch.ones(4))
+    th = T.Theta({"ffn_norm": {"weight": w}, "ffn_gate_inp": {"weight": w, "bias": w}})
+    assert th.tensor("ffn_norm", "weight") is w
+    assert th("ffn_gate_inp").tensor("bias") is w
+    assert th.optional_tensor("layer_output_norm") is None
+    assert th.optional_tensor("ffn_norm") is not None
+    assert "bias" in th("ffn_gate_inp").keys
+    with pytest.raises(KeyError):
+        th.tensor("nope", "weight")
+
+
+def test_product_never_imports_the_oracle():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pkg = os.path.join(root, "shark_platform_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("# oracle", ""), f"{f} mentions the oracle"
+
+
+REF = "/root/reference/sharktank"
+
+
+@pytest.mark.skipif(not os.path.isdir(REF), reason="sharktank checkout not present")
+def test_plugin_registers_ahead_of_sharktank_overrides():
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    sys.path.insert(0, REF)
+    import iree_stub
+
+    iree_stub.install()
+    import sharktank.ops as st_ops
+    from sharktank.types import PlanarQuantizedTensor
+    from sharktank.types.layouts import BlockScaledLayout
+
+    from shark_platform_b200 import moe, plugin
+
+    plugin.register()
+    lay = BlockScaledLayout([2, 64, 256], torch.zeros(2, 64, 8, 1, dtype=torch.float16),
+                            torch.zeros(2, 64, 8, 32, dtype=torch.int8))
+    q = PlanarQuantizedTensor(shape=[2, 64, 256], layout=lay)
+    first = next(iter(st_ops.get_index.find_overrides((q,))))
+    assert first is moe.get_index_quantized
+    g = moe.GatheredExperts(q, torch.zeros(3, 2, dtype=torch.int64))
+    first = next(iter(st_ops.einsum_2args.find_overrides((torch.zeros(1), g))))
+    assert first is moe.einsum_2args_gathered
+    # CPU tensors: our overrides decline and the reference's own error surfaces
+    with pytest.raises(NotImplementedError):
+        q[torch.zeros(3, 2, dtype=torch.int64), :, :]
