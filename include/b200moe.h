@@ -183,6 +183,15 @@ int b200moe_layer_forward_host(const b200moe_layer_t* layer, const void* h_host,
                                int io_dtype, int32_t tokens, int regime, void* dev_io,
                                void* workspace, size_t workspace_bytes, void* stream);
 
+/* Stage timing for benchmarks (no reference counterpart).  While enabled,
+ * b200moe_layer_forward brackets each of its six stages (router, route plan,
+ * permute, gate/up, down, combine) with CUDA events on the call's stream; up to
+ * 512 calls are kept.  b200moe_profile_read synchronises those events, adds the
+ * per-stage milliseconds of all recorded calls into ms_out[6], returns the
+ * number of calls through *calls_out and clears the record. */
+int b200moe_profile_enable(int on);
+int b200moe_profile_read(float* ms_out, int32_t* calls_out);
+
 #ifdef __cplusplus
 }
 #endif

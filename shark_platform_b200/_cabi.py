@@ -94,6 +94,8 @@ _PROTOS = {
     "b200moe_workspace_bytes": (c_size_t, [_L, c_int32]),
     "b200moe_layer_forward": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, c_size_t, _P, _P, _P]),
     "b200moe_layer_forward_host": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, _P, c_size_t, _P]),
+    "b200moe_profile_enable": (c_int, [c_int]),
+    "b200moe_profile_read": (c_int, [POINTER(c_float), POINTER(c_int32)]),
 }
 
 for _name, (_res, _args) in _PROTOS.items():

@@ -173,6 +173,21 @@ int check_layer(const b200moe_layer_t* L) {
   return B200MOE_OK;
 }
 
+// Stage profiler: a ring of event sets, one set of 7 events per recorded call.
+constexpr int PROF_STAGES = 6;
+constexpr int PROF_CALLS = 512;
+struct Profiler {
+  bool on = false;
+  int used = 0;
+  cudaEvent_t ev[PROF_CALLS][PROF_STAGES + 1] = {};
+  bool created = false;
+};
+Profiler g_prof;
+
+inline void prof_mark(int call, int idx, cudaStream_t st) {
+  if (call >= 0) cudaEventRecord(g_prof.ev[call][idx], st);
+}
+
 }  // namespace
 }  // namespace b200moe
 
@@ -327,21 +342,29 @@ int b200moe_layer_forward(const b200moe_layer_t* L, const void* h, void* y, int 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int pairs = tokens * L->top_k;
   const int E = L->experts;
+  const int pc = (g_prof.on && g_prof.used < PROF_CALLS) ? g_prof.used++ : -1;
+  prof_mark(pc, 0, st);
   if (int rc = launch_router(h, io_dtype, tokens, L, w.xn, w.experts, w.gates, st)) return rc;
+  prof_mark(pc, 1, st);
   if (int rc = launch_route_plan(w.experts, pairs, 0, E, w.counts, w.seg, w.perm, w.inv, st))
     return rc;
+  prof_mark(pc, 2, st);
   const int kp_in = b200moe_kperm(L->gate.layout, regime, tokens);
   const int kp_mid = b200moe_kperm(L->down.layout, regime, tokens);
   if (int rc = launch_permute_rows(w.xn, w.perm, w.seg, E, pairs, L->top_k, L->hidden, kp_in, w.xs, st))
     return rc;
+  prof_mark(pc, 3, st);
   if (int rc = b200moe_gate_up(w.xs, w.seg, pairs, tokens, &L->gate, &L->up, L->activation, regime,
                                kp_mid, w.a, stream))
     return rc;
+  prof_mark(pc, 4, st);
   const int ks = b200moe_down_ksplit(&L->down, pairs, tokens, regime);
   if (int rc = b200moe_down(w.a, w.seg, pairs, tokens, &L->down, regime, w.dpart, stream)) return rc;
+  prof_mark(pc, 5, st);
   if (int rc = launch_combine(w.dpart, ks, pairs, w.inv, w.gates, h, io_dtype, tokens, L, 1, y,
                               io_dtype, st))
     return rc;
+  prof_mark(pc, 6, st);
   if (experts_out)
     B200_CHECK_CUDA(cudaMemcpyAsync(experts_out, w.experts, sizeof(int32_t) * pairs,
                                     cudaMemcpyDeviceToDevice, st));
@@ -369,6 +392,33 @@ int b200moe_layer_forward_host(const b200moe_layer_t* L, const void* h_host, voi
                                      workspace_bytes, nullptr, nullptr, stream))
     return rc;
   B200_CHECK_CUDA(cudaMemcpyAsync(y_host, dy, bytes, cudaMemcpyDeviceToHost, st));
+  return B200MOE_OK;
+}
+
+int b200moe_profile_enable(int on) {
+  if (on && !g_prof.created) {
+    for (int c = 0; c < PROF_CALLS; ++c)
+      for (int i = 0; i <= PROF_STAGES; ++i) B200_CHECK_CUDA(cudaEventCreate(&g_prof.ev[c][i]));
+    g_prof.created = true;
+  }
+  g_prof.on = on != 0;
+  g_prof.used = 0;
+  return B200MOE_OK;
+}
+
+int b200moe_profile_read(float* ms_out, int32_t* calls_out) {
+  B200_REQUIRE(ms_out && calls_out, "profile_read: NULL argument");
+  for (int i = 0; i < PROF_STAGES; ++i) ms_out[i] = 0.f;
+  for (int c = 0; c < g_prof.used; ++c) {
+    B200_CHECK_CUDA(cudaEventSynchronize(g_prof.ev[c][PROF_STAGES]));
+    for (int i = 0; i < PROF_STAGES; ++i) {
+      float ms = 0.f;
+      B200_CHECK_CUDA(cudaEventElapsedTime(&ms, g_prof.ev[c][i], g_prof.ev[c][i + 1]));
+      ms_out[i] += ms;
+    }
+  }
+  *calls_out = g_prof.used;
+  g_prof.used = 0;
   return B200MOE_OK;
 }
 

@@ -401,7 +401,9 @@ __global__ void dequant_q4k_kernel(const uint8_t* __restrict__ qs, const __half2
   const uint8_t b = qs[i >> 1];
   const int q = (i & 1) ? (b >> 4) : (b & 0xF);
   const __half2 sm = sub[i >> 5];
-  const __half w = __hsub(__hmul(__low2half(sm), __int2half_rn(q)), __high2half(sm));
+  // the _rn forms are never contracted into an fma: the reference rounds after
+  // the product and again after the subtraction
+  const __half w = __hsub_rn(__hmul_rn(__low2half(sm), __int2half_rn(q)), __high2half(sm));
   if constexpr (sizeof(TO) == 2) {
     out[i] = w;
   } else {

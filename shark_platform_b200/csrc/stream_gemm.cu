@@ -88,7 +88,7 @@ __device__ __forceinline__ void dequant_q4x8(uint32_t w, __half2 ds, __half2 dm,
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const __half2 q = __hsub2(u32_as_h2(e[i]), k1024);
-    out[i] = h2_as_u32(__hsub2(__hmul2(ds, q), dm));
+    out[i] = h2_as_u32(__hsub2_rn(__hmul2_rn(ds, q), dm));  // _rn: no fma contraction
   }
 }
 

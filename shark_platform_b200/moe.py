@@ -313,7 +313,8 @@ class B200MoeBlock(torch.nn.Module):
         _LAYERS[self._handle] = self.layer
 
     def __del__(self):
-        _LAYERS.pop(getattr(self, "_handle", None), None)
+        if _LAYERS is not None:
+            _LAYERS.pop(getattr(self, "_handle", None), None)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return torch.ops.b200moe.layer_forward(h, self._handle, self.regime)

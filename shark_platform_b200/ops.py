@@ -97,11 +97,12 @@ def get_index(tensor, key):
     (sharktank/ops/signatures.py:317-340)."""
 
 
-@overridable(0)
+@overridable(1)
 def elementwise(operator, *args, **kwargs):
     """Applies an elementwise operator (sharktank/ops/signatures.py:209-228)."""
 
 
 @elementwise.override(torch.Tensor)
 def _elementwise_tensor(operator, x, *args, **kwargs):
+    # ops/default_impls.py:125-128
     return operator(x, *args, **kwargs)
