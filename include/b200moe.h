@@ -155,6 +155,25 @@ int b200moe_down_ksplit(const b200moe_weight_t* down, int32_t pairs, int32_t max
 int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32_t max_segment,
                  const b200moe_weight_t* down, int regime, float* d_out, void* stream);
 
+/* No counterpart in the reference.  The same down projection as b200moe_down
+ * for hosts that cannot allocate device memory where they call the layer (an
+ * allocator's own callback, a runtime that owns the whole device heap, a decode
+ * loop that bans allocator calls): the k-split partial sums live in an 8 MiB
+ * array built into the library (held by every GPU that loads it until the
+ * process exits) and the caller receives the finished sums.
+ * d_out: fp32 [pairs, d]; rows at and after seg_offsets[experts] are set to 0.
+ * Limit: ksplit * pairs * d <= 2,097,152 floats with ksplit =
+ * b200moe_down_ksplit(...) (e.g. 128 pairs at d = 4096); larger calls fail with
+ * B200MOE_ERR_INVALID and a message.  Calls no cudaMalloc / cudaFree.
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress): make that first call outside any stream capture.
+ * All calls share the one array and nothing in it needs clearing between
+ * calls (every partial that is read was written by the same call), but two
+ * calls that overlap on the GPU (different streams) race on it. */
+int b200moe_down_noalloc(const void* a, const int32_t* seg_offsets, int32_t pairs,
+                         int32_t max_segment, const b200moe_weight_t* down, float* d_out,
+                         void* stream);
+
 /* y[t] = h[t] + norm?( sum_slot gates[t,slot] * D[inv[t*k+slot]] ): the
  * "me,men->men" scaling and torch.sum over slots (layers/ffn_moe_block.py:
  * 73-74), the optional layer_output_norm and the residual
