@@ -75,46 +75,64 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint32_t elem_bytes,
-                 uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
-                 bool swizzle128) {
+int make_tmap_2d_sw(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes,
+                    uint32_t box_rows, uint32_t box_bytes, int swizzle_bytes) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) {
     set_error("cuTensorMapEncodeTiled is not available from the driver");
     return B200MOE_ERR_CUDA;
   }
   B200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor map base misaligned");
-  B200_REQUIRE((cols * elem_bytes) % 16 == 0, "tensor map row pitch must be a multiple of 16 bytes");
-  B200_REQUIRE(box_rows >= 1 && box_rows <= 256 && box_cols >= 1 && box_cols <= 256 &&
-                   (box_cols * elem_bytes) % 16 == 0,
+  B200_REQUIRE(row_bytes % 16 == 0, "tensor map row pitch must be a multiple of 16 bytes");
+  B200_REQUIRE(box_rows >= 1 && box_rows <= 256 && box_bytes >= 16 && box_bytes <= 256 &&
+                   box_bytes % 16 == 0,
                "tensor map box out of range");
-  B200_REQUIRE(!swizzle128 || box_cols * elem_bytes == 128, "128B swizzle needs a 128-byte box row");
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * elem_bytes};
-  const cuuint32_t box[2] = {box_cols, box_rows};
+  CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+  if (swizzle_bytes == 32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
+  else if (swizzle_bytes == 64) sw = CU_TENSOR_MAP_SWIZZLE_64B;
+  else if (swizzle_bytes == 128) sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  else B200_REQUIRE(swizzle_bytes == 0, "tensor map swizzle must be 0, 32, 64 or 128");
+  B200_REQUIRE(swizzle_bytes == 0 || box_bytes <= static_cast<uint32_t>(swizzle_bytes),
+               "tensor map box row wider than the swizzle span");
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {box_bytes, box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r =
-      fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled failed with %d (rows=%llu cols=%llu box=%ux%u)",
+    set_error("cuTensorMapEncodeTiled failed with %d (rows=%llu row_bytes=%llu box=%ux%u)",
               static_cast<int>(r), static_cast<unsigned long long>(rows),
-              static_cast<unsigned long long>(cols), box_rows, box_cols);
+              static_cast<unsigned long long>(row_bytes), box_rows, box_bytes);
     return B200MOE_ERR_CUDA;
   }
   return B200MOE_OK;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint32_t elem_bytes,
+                 uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
+                 bool swizzle128) {
+  (void)dt;
+  B200_REQUIRE(!swizzle128 || box_cols * elem_bytes == 128, "128B swizzle needs a 128-byte box row");
+  return make_tmap_2d_sw(out, base, rows, cols * elem_bytes, box_rows, box_cols * elem_bytes,
+                         swizzle128 ? 128 : 0);
 }
 
 namespace {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Above this many tokens the tensor-memory kernel takes over from the
+// weight-streaming kernel (where the layout allows it).
+constexpr int TENSOR_MIN_TOKENS = 129;
+
 int pick_regime(int regime, const b200moe_weight_t* w, int max_segment) {
-  (void)w;
-  (void)max_segment;
+  const bool can_tensor = w != nullptr && tc_supported(w);
   if (regime == B200MOE_REGIME_TENSOR) return B200MOE_REGIME_TENSOR;
-  return B200MOE_REGIME_STREAM;
+  if (regime == B200MOE_REGIME_STREAM) return B200MOE_REGIME_STREAM;
+  return (can_tensor && max_segment >= TENSOR_MIN_TOKENS) ? B200MOE_REGIME_TENSOR
+                                                          : B200MOE_REGIME_STREAM;
 }
 
 // Workspace carve-up of one layer call.
@@ -136,7 +154,7 @@ Workspace carve(const b200moe_layer_t* L, int tokens, void* base) {
   const size_t T = tokens > 0 ? tokens : 1;
   const size_t P = T * L->top_k;
   const size_t d = L->hidden, F = L->ffn;
-  const int ks = stream_down_ksplit(&L->down, static_cast<int>(P));
+  const int ks = stream_down_ksplit(&L->down, static_cast<int>(P));  // >= the tensor regime's 1
   uint8_t* p = static_cast<uint8_t*>(base);
   size_t off = 0;
   auto take = [&](size_t n) {
@@ -271,8 +289,10 @@ int b200moe_permute_rows(const void* xn, const int32_t* perm, const int32_t* seg
 }
 
 int b200moe_kperm(int layout, int regime, int32_t max_segment) {
-  const int r = pick_regime(regime, nullptr, max_segment);
-  return (layout == B200MOE_LAYOUT_Q4_K && r == B200MOE_REGIME_STREAM) ? 1 : 0;
+  (void)regime;
+  (void)max_segment;
+  // Q4_K runs in the streaming kernel only, which wants interleaved columns.
+  return layout == B200MOE_LAYOUT_Q4_K ? 1 : 0;
 }
 
 int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
@@ -284,7 +304,11 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
   B200_REQUIRE(activation == B200MOE_ACT_SILU || activation == B200MOE_ACT_GELU,
                "gate_up: unknown activation %d", activation);
   const int r = pick_regime(regime, gate, max_segment);
-  B200_REQUIRE(r == B200MOE_REGIME_STREAM, "gate_up: tensor regime not available in this build");
+  if (r == B200MOE_REGIME_TENSOR) {
+    B200_REQUIRE(!out_kperm, "gate_up: the tensor regime writes natural column order");
+    return launch_tc_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, a_out,
+                             static_cast<cudaStream_t>(stream));
+  }
   return launch_stream_gate_up(xs, seg_offsets, pairs, max_segment, gate, up, activation,
                                out_kperm, a_out, static_cast<cudaStream_t>(stream));
 }
@@ -301,7 +325,8 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
   B200_REQUIRE(down && seg_offsets, "down: NULL argument");
   B200_REQUIRE(pairs == 0 || (a && d_out), "down: NULL buffer");
   const int r = pick_regime(regime, down, max_segment);
-  B200_REQUIRE(r == B200MOE_REGIME_STREAM, "down: tensor regime not available in this build");
+  if (r == B200MOE_REGIME_TENSOR)
+    return launch_tc_down(a, seg_offsets, pairs, 128, down, d_out, static_cast<cudaStream_t>(stream));
   return launch_stream_down(a, seg_offsets, pairs, max_segment, down,
                             stream_down_ksplit(down, pairs), d_out,
                             static_cast<cudaStream_t>(stream));

@@ -40,6 +40,11 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uin
                  uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
                  bool swizzle128);
 
+// Same over a byte array: row_bytes per row, a box of box_rows x box_bytes and
+// a shared-memory swizzle of 0, 32, 64 or 128 bytes (box_bytes <= swizzle).
+int make_tmap_2d_sw(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes,
+                    uint32_t box_rows, uint32_t box_bytes, int swizzle_bytes);
+
 // Error bits written to the device status word.
 enum : int32_t {
   DEV_ERR_WAIT_TIMEOUT = 1,  // a bounded mbarrier wait gave up

@@ -30,4 +30,12 @@ int launch_stream_gate_up(const void* xs, const int32_t* seg, int pairs, int max
 int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_segment,
                        const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st);
 
+// prefill regime (tc_gemm.cu)
+bool tc_supported(const b200moe_weight_t* w);
+int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_tile,
+                      const b200moe_weight_t* gate, const b200moe_weight_t* up, int act,
+                      void* a_out, cudaStream_t st);
+int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile,
+                   const b200moe_weight_t* down, float* d_out, cudaStream_t st);
+
 }  // namespace b200moe

@@ -1,0 +1,445 @@
+// Tensor-core grouped expert GEMM for the prefill regime (many tokens per
+// expert): tcgen05.mma with fp32 accumulators in tensor memory.
+//
+// Orientation is "swap-AB" with the A operand in tensor memory: a tile of 128
+// weight rows is M, up to 192 tokens of one expert are N.  Weights never touch
+// shared memory in dequantised form: two warpgroups read the TMA-staged
+// quantised bytes (one thread per weight row), dequantise to fp16 in registers
+// and write the row into tensor memory with tcgen05.st, where it is the A
+// operand of the next MMAs.  The token rows (fp16, K-major, 128-byte swizzle) are
+// the B operand, read from shared memory through a matrix descriptor.  This
+// keeps shared-memory traffic at (quantised bytes + token tile reads), well
+// under the 128 B/clk that an SS-mode MMA with in-smem dequantisation exceeds.
+//
+// A CTA holds two row sets per tile, each with its own accumulator:
+// gate rows + up rows of the same 128 columns (SiLU/GELU-gated product in the
+// epilogue), or 256 consecutive rows of the down matrix.
+//
+// Warp roles (320 threads, one CTA per SM, persistent over tiles):
+//   warps 0-3  dequantise set 0, then epilogue     (TMEM lanes 32w..32w+31)
+//   warps 4-7  dequantise set 1, then epilogue
+//   warp  8    TMA producer (quantised tiles + token tile per 64-k stage)
+//   warp  9    TMEM allocation; one lane issues the MMAs and commits
+//
+// Tensor-memory columns (512 allocated): accumulators at 0 and 192 (192 fp32
+// columns each), two A staging slots of 2 x 32 columns at 384..511.
+//
+// All mbarrier waits are bounded; on expiry the CTA raises its abort flag, every
+// role falls out of its loops, the CTA frees its tensor memory and returns.
+#include "common.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int TC_THREADS = 320;
+constexpr int TC_KT = 64;          // k per stage
+constexpr int TC_ROWS = 128;       // weight rows per set
+constexpr int TC_NTOK = 192;       // token rows of the staged tile / accumulator columns
+constexpr int TC_MAX_E = 64;
+constexpr int TC_WSET = TC_ROWS * TC_KT;        // quantised bytes per set per stage (Q8_0)
+constexpr int TC_XTILE = TC_NTOK * TC_KT * 2;   // token tile bytes per stage
+constexpr int TC_STAGE = 2 * TC_WSET + TC_XTILE;
+constexpr int TC_STAGES = 5;
+constexpr int TC_SMEM = 1024 + TC_STAGES * TC_STAGE + 256;
+constexpr uint32_t TC_COL_ACC0 = 0, TC_COL_ACC1 = 192, TC_COL_A = 384;
+static_assert(TC_STAGE % 1024 == 0, "stage alignment");
+static_assert(TC_SMEM <= 232448, "shared memory budget");
+
+struct TcArgs {
+  const int32_t* seg;
+  int E, N, K;
+  int ntiles;      // row tiles per expert (N / 128 for gate+up, N / 256 for down)
+  int tok_tile;    // upper bound on tokens per tile (multiple of 16, <= 192)
+  int P;
+  int act;
+  const __half* d0;  // block scales of set 0's matrix  [E*N, K/32]
+  const __half* d1;  // block scales of set 1's matrix (gate/up: the up matrix)
+  void* out;
+  int32_t* status;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+      "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),
+      "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]),
+      "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]),
+      "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
+// 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);          // start address
+  d |= static_cast<uint64_t>(1024u >> 4) << 32;                // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                         // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                         // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major.
+__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+template <int NMAT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
+               const __grid_constant__ CUtensorMap tm_x, const TcArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_seg[TC_MAX_E + 1];
+  __shared__ int s_prefix[TC_MAX_E + 1];
+  __shared__ int s_abort;
+  __shared__ uint32_t s_tmem;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + TC_STAGES * TC_STAGE;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (TC_STAGES + s); };
+  auto a_ready_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + s); };
+  auto a_free_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + 2 + s); };
+  const uint32_t acc_full_bar = bar_base + 8u * (2 * TC_STAGES + 4);
+  const uint32_t acc_empty_bar = bar_base + 8u * (2 * TC_STAGES + 5);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 8 + 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(a_ready_bar(s), 256);
+      mbar_init(a_free_bar(s), 1);
+    }
+    mbar_init(acc_full_bar, 1);
+    mbar_init(acc_empty_bar, 256);
+    fence_mbar_init();
+    int run = 0;
+    for (int e = 0; e < args.E; ++e) {
+      const int a = args.seg[e], b = args.seg[e + 1];
+      s_seg[e] = a;
+      s_prefix[e] = run;
+      run += ((b - a + args.tok_tile - 1) / args.tok_tile) * args.ntiles;
+    }
+    s_seg[args.E] = args.seg[args.E];
+    s_prefix[args.E] = run;
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&s_tmem), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+  const int total_tiles = s_prefix[args.E];
+  volatile int* abort_flag = &s_abort;
+  const int stages_per_tile = args.K / TC_KT;
+
+  // tile -> (expert, row tile, first token row, token rows, MMA N)
+  auto decode = [&](int tile, int& e, int& nt, int& row0, int& rows, int& ncols) {
+    e = 0;
+    while (tile >= s_prefix[e + 1]) ++e;
+    const int local = tile - s_prefix[e];
+    const int m = s_seg[e + 1] - s_seg[e];
+    const int mtiles = (m + args.tok_tile - 1) / args.tok_tile;
+    const int mt = local % mtiles;
+    nt = local / mtiles;
+    const int per = ((m + mtiles - 1) / mtiles + 15) & ~15;  // balanced, multiple of 16
+    row0 = s_seg[e] + mt * per;
+    rows = min(per, s_seg[e + 1] - row0);
+    if (rows < 0) rows = 0;
+    ncols = (max(rows, 1) + 15) & ~15;
+  };
+
+  if (warp == 8) {
+    // ---------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t n = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int e, nt, row0, rows, ncols;
+        decode(tile, e, nt, row0, rows, ncols);
+        const int grow0 = e * args.N + nt * (NMAT == 2 ? TC_ROWS : 2 * TC_ROWS);
+        for (int st = 0; st < stages_per_tile; ++st, ++n) {
+          const int slot = n % TC_STAGES;
+          const uint32_t ph = (n / TC_STAGES) & 1u;
+          if (!mbar_wait(empty_bar(slot), ph ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          const uint32_t sb = smem_base + slot * TC_STAGE;
+          const uint32_t fb = full_bar(slot);
+          mbar_expect_tx(fb, TC_STAGE);
+          const int k0 = st * TC_KT;
+          tma_load_2d(sb, &tm_w0, k0, grow0, fb);
+          tma_load_2d(sb + TC_WSET, NMAT == 2 ? &tm_w1 : &tm_w0, k0,
+                      NMAT == 2 ? grow0 : grow0 + TC_ROWS, fb);
+          tma_load_2d(sb + 2 * TC_WSET, &tm_x, k0 * 2, row0, fb);
+        }
+      }
+      const uint32_t first = n > (uint32_t)TC_STAGES ? n - TC_STAGES : 0;
+      for (uint32_t i = first; i < n; ++i)
+        mbar_wait(full_bar(i % TC_STAGES), (i / TC_STAGES) & 1u, abort_flag, args.status);
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t n = 0, ti = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
+        int e, nt, row0, rows, ncols;
+        decode(tile, e, nt, row0, rows, ncols);
+        const uint32_t idesc = make_idesc(128, ncols);
+        if (!mbar_wait(acc_empty_bar, (ti & 1u) ^ 1u, abort_flag, args.status)) break;
+        tc_fence_after();
+        for (int st = 0; st < stages_per_tile; ++st, ++n) {
+          const int slot = n % TC_STAGES;
+          const int as = n & 1;
+          if (!mbar_wait(full_bar(slot), (n / TC_STAGES) & 1u, abort_flag, args.status) ||
+              !mbar_wait(a_ready_bar(as), (n >> 1) & 1u, abort_flag, args.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t xaddr = smem_base + slot * TC_STAGE + 2 * TC_WSET;
+          const uint64_t bdesc = smem_desc_sw128(xaddr);
+#pragma unroll
+          for (int j = 0; j < TC_KT / 16; ++j) {
+            const uint32_t accum = (st > 0 || j > 0) ? 1u : 0u;
+            const uint64_t bd = bdesc + static_cast<uint64_t>((j * 32) >> 4);
+            const uint32_t a0 = tmem + TC_COL_A + as * 64 + j * 8;
+            tc_mma_ts(tmem + TC_COL_ACC0, a0, bd, idesc, accum);
+            tc_mma_ts(tmem + TC_COL_ACC1, a0 + 32, bd, idesc, accum);
+          }
+          tc_commit(empty_bar(slot));
+          tc_commit(a_free_bar(as));
+        }
+        if (ok) tc_commit(acc_full_bar);
+      }
+    }
+  } else {
+    // ------------------------------------- dequantise (both sets) + epilogue
+    const int set = warp >> 2;              // 0: warps 0-3, 1: warps 4-7
+    const int wq = warp & 3;                // TMEM lane quarter
+    const int row = wq * 32 + lane;         // weight row within the set = TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
+    const int sw = (row >> 1) & 3;          // 64-byte swizzle term of this row
+    const __half* dbase = (NMAT == 2 && set == 1) ? args.d1 : args.d0;
+    const int kblocks = args.K / 32;
+    uint32_t n = 0, ti = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
+      int e, nt, row0, rows, ncols;
+      decode(tile, e, nt, row0, rows, ncols);
+      const int grow = e * args.N + nt * (NMAT == 2 ? TC_ROWS : 2 * TC_ROWS) +
+                       (NMAT == 2 ? 0 : set * TC_ROWS) + row;
+      const uint4* srow = reinterpret_cast<const uint4*>(dbase + static_cast<size_t>(grow) * kblocks);
+      uint4 sc_next = srow[0];
+      for (int sg = 0; sg < stages_per_tile / 4 && ok; ++sg) {
+        const uint4 sc4 = sc_next;
+        if (sg + 1 < stages_per_tile / 4) sc_next = srow[sg + 1];
+        const uint32_t scw[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4, ++n) {
+          const int slot = n % TC_STAGES;
+          const int as = n & 1;
+          if (!mbar_wait(full_bar(slot), (n / TC_STAGES) & 1u, abort_flag, args.status)) { ok = false; break; }
+          const uint32_t wrow = smem_base + slot * TC_STAGE + set * TC_WSET + row * 64;
+          uint32_t q[4][4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) lds128(wrow + ((c ^ sw) << 4), q[c]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty_bar(slot));
+          uint32_t v[32];
+          const __half2 s_lo = u32_as_h2(__byte_perm(scw[s4], scw[s4], 0x1010));
+          const __half2 s_hi = u32_as_h2(__byte_perm(scw[s4], scw[s4], 0x3232));
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              dequant_q8x4(q[c][j], c < 2 ? s_lo : s_hi, v[c * 8 + 2 * j], v[c * 8 + 2 * j + 1]);
+          if (!mbar_wait(a_free_bar(as), ((n >> 1) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          tc_fence_after();
+          tmem_st32(tmem + lane_addr + TC_COL_A + as * 64 + set * 32, v);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(a_ready_bar(as));
+        }
+      }
+      if (!ok) break;
+      // ---- epilogue: this warpgroup takes every other 16-token column chunk
+      if (!mbar_wait(acc_full_bar, ti & 1u, abort_flag, args.status)) break;
+      tc_fence_after();
+      const int seg_end = row0 + rows;
+      for (int c0 = set * 16; c0 < ncols; c0 += 32) {
+        uint32_t g[16], u[16];
+        tmem_ld16(tmem + lane_addr + TC_COL_ACC0 + c0, g);
+        tmem_ld16(tmem + lane_addr + TC_COL_ACC1 + c0, u);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int tok = row0 + c0 + j;
+          if (tok >= seg_end) continue;
+          if constexpr (NMAT == 2) {
+            const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+            const float a = args.act == B200MOE_ACT_SILU ? silu_f(gv) : gelu_erf_f(gv);
+            static_cast<__half*>(args.out)[static_cast<size_t>(tok) * args.N + nt * TC_ROWS + row] =
+                to_half_sat(a * uv);
+          } else {
+            float* o = static_cast<float*>(args.out) + static_cast<size_t>(tok) * args.N +
+                       nt * (2 * TC_ROWS) + row;
+            o[0] = __uint_as_float(g[j]);
+            o[TC_ROWS] = __uint_as_float(u[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty_bar);
+    }
+  }
+
+  // ---- teardown: everyone is done with tensor memory before it is freed
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int NMAT>
+int tc_launch(const CUtensorMap* maps, const TcArgs& a, cudaStream_t st) {
+  auto kern = tc_gemm_kernel<NMAT>;
+  static bool configured[16] = {};
+  int dev = 0;
+  B200_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 16 && !configured[dev]) {
+    B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
+    configured[dev] = true;
+  }
+  kern<<<sm_count(), TC_THREADS, TC_SMEM, st>>>(maps[0], maps[1], maps[2], a);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int tc_check(const b200moe_weight_t* w, const char* name) {
+  B200_REQUIRE(w->layout == B200MOE_LAYOUT_Q8_0, "tensor kernel: %s must be Q8_0 (layout %d)", name,
+               w->layout);
+  B200_REQUIRE(w->cols % 256 == 0, "tensor kernel: %s cols (%d) must be a multiple of 256", name,
+               w->cols);
+  B200_REQUIRE(w->experts >= 1 && w->experts <= TC_MAX_E, "tensor kernel: %s experts out of range", name);
+  B200_REQUIRE(w->qs && w->d && (reinterpret_cast<uintptr_t>(w->qs) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(w->d) & 15) == 0,
+               "tensor kernel: %s planes missing or misaligned", name);
+  return B200MOE_OK;
+}
+
+int tc_weight_map(const b200moe_weight_t* w, CUtensorMap* tw) {
+  // 64-byte wide boxes of int8 with the 64-byte swizzle: 128 rows x 64 k
+  const uint64_t rows = static_cast<uint64_t>(w->experts) * w->rows;
+  return make_tmap_2d_sw(tw, w->qs, rows, w->cols, TC_ROWS, 64, 64);
+}
+
+}  // namespace
+
+bool tc_supported(const b200moe_weight_t* w) {
+  return w->layout == B200MOE_LAYOUT_Q8_0 && w->cols % 256 == 0;
+}
+
+int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_tile,
+                      const b200moe_weight_t* gate, const b200moe_weight_t* up, int act,
+                      void* a_out, cudaStream_t st) {
+  if (int rc = tc_check(gate, "gate")) return rc;
+  if (int rc = tc_check(up, "up")) return rc;
+  B200_REQUIRE(gate->rows == up->rows && gate->cols == up->cols && gate->experts == up->experts,
+               "tensor kernel: gate and up shapes differ");
+  B200_REQUIRE(gate->rows % TC_ROWS == 0, "tensor kernel: ffn (%d) must be a multiple of 128", gate->rows);
+  if (pairs == 0) return B200MOE_OK;
+  CUtensorMap maps[3];
+  if (int rc = tc_weight_map(gate, &maps[0])) return rc;
+  if (int rc = tc_weight_map(up, &maps[1])) return rc;
+  if (int rc = make_tmap_2d_sw(&maps[2], xs, pairs, static_cast<uint64_t>(gate->cols) * 2, TC_NTOK, 128, 128))
+    return rc;
+  TcArgs a{};
+  a.seg = seg; a.E = gate->experts; a.N = gate->rows; a.K = gate->cols;
+  a.ntiles = gate->rows / TC_ROWS; a.tok_tile = tok_tile; a.P = pairs; a.act = act;
+  a.d0 = static_cast<const __half*>(gate->d); a.d1 = static_cast<const __half*>(up->d);
+  a.out = a_out; a.status = device_status_ptr();
+  if (a.status == nullptr) return B200MOE_ERR_CUDA;
+  return tc_launch<2>(maps, a, st);
+}
+
+int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile,
+                   const b200moe_weight_t* down, float* d_out, cudaStream_t st) {
+  if (int rc = tc_check(down, "down")) return rc;
+  B200_REQUIRE(down->rows % (2 * TC_ROWS) == 0, "tensor kernel: hidden (%d) must be a multiple of 256",
+               down->rows);
+  if (pairs == 0) return B200MOE_OK;
+  CUtensorMap maps[3];
+  if (int rc = tc_weight_map(down, &maps[0])) return rc;
+  maps[1] = maps[0];
+  if (int rc = make_tmap_2d_sw(&maps[2], a_in, pairs, static_cast<uint64_t>(down->cols) * 2, TC_NTOK, 128, 128))
+    return rc;
+  TcArgs a{};
+  a.seg = seg; a.E = down->experts; a.N = down->rows; a.K = down->cols;
+  a.ntiles = down->rows / (2 * TC_ROWS); a.tok_tile = tok_tile; a.P = pairs; a.act = 0;
+  a.d0 = static_cast<const __half*>(down->d); a.d1 = a.d0;
+  a.out = d_out; a.status = device_status_ptr();
+  if (a.status == nullptr) return B200MOE_ERR_CUDA;
+  return tc_launch<1>(maps, a, st);
+}
+
+}  // namespace b200moe

@@ -232,3 +232,39 @@ def test_ops_decline_unsupported():
     t = T.DefaultPrimitiveTensor(data=torch.zeros(2, 2))
     with pytest.raises(NotImplementedError):
         ops.get_index(t, (torch.zeros(1, 1, dtype=torch.int64), slice(None), slice(None)))
+
+
+# ------------------------------------------------ tensor-memory (tcgen05) regime
+@pytest.mark.parametrize("name", ["small_q8", "small_grok", "small_top4"])
+def test_tensor_regime_matches_reference_fixture(M, name):
+    g = load_golden(f"moe_{name}.npz")
+    case = syn.make_case(syn.CASES[name])
+    blk = b200_block(case, regime="tensor")
+    y = blk(device_input(case)).float().cpu()
+    assert M.device_status() == 0
+    assert orc.rel_l2(y, torch.from_numpy(g["y"])) < REL_L2_TOL
+    y2 = blk(device_input(case)).float().cpu()
+    assert torch.equal(y, y2), "two runs differ: a race"
+
+
+@pytest.mark.parametrize("tokens", [1, 15, 16, 17, 100, 193, 400, 777])
+def test_tensor_regime_ragged_token_counts(M, tokens):
+    spec = syn.CaseSpec("ragged_tc", tokens, 512, 1024, kind=syn.Q8_0, norm_weight="perturbed",
+                        seed=300 + tokens, act_dtype="f32")
+    case = syn.make_case(spec)
+    want, mid = orc.moe_block(case.h, oracle_params(case), form="per_expert")
+    blk = b200_block(case, regime="tensor")
+    y = blk.layer.forward(case.h.cuda(), regime=M.REGIMES["tensor"])
+    assert M.device_status() == 0
+    assert orc.rel_l2(y.cpu() - case.h, want - case.h) < REL_L2_TOL
+
+
+def test_tensor_and_stream_regimes_agree(M):
+    """Same operands, same fp32 accumulation up to summation order."""
+    spec = syn.CaseSpec("agree", 300, 512, 1024, kind=syn.Q8_0, seed=9, act_dtype="f32")
+    case = syn.make_case(spec)
+    blk = b200_block(case)
+    h = case.h.cuda()
+    ys = blk.layer.forward(h, regime=M.REGIMES["stream"]).cpu()
+    yt = blk.layer.forward(h, regime=M.REGIMES["tensor"]).cpu()
+    assert orc.rel_l2(yt - case.h, ys - case.h) < 1e-3
