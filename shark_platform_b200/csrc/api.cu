@@ -125,7 +125,7 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Above this many tokens the tensor-memory kernel takes over from the
 // weight-streaming kernel (where the layout allows it).
-constexpr int TENSOR_MIN_TOKENS = 129;
+constexpr int TENSOR_MIN_TOKENS = 97;
 
 int pick_regime(int regime, const b200moe_weight_t* w, int max_segment) {
   const bool can_tensor = w != nullptr && tc_supported(w);

@@ -15,11 +15,13 @@
 // gate rows + up rows of the same 128 columns (SiLU/GELU-gated product in the
 // epilogue), or 256 consecutive rows of the down matrix.
 //
-// Warp roles (320 threads, one CTA per SM, persistent over tiles):
-//   warps 0-3  dequantise set 0, then epilogue     (TMEM lanes 32w..32w+31)
-//   warps 4-7  dequantise set 1, then epilogue
-//   warp  8    TMA producer (quantised tiles + token tile per 64-k stage)
-//   warp  9    TMEM allocation; one lane issues the MMAs and commits
+// Warp roles (576 threads, one CTA per SM, persistent over tiles):
+//   warps 0-7   group 0: dequantise the even 64-k stages (warps 0-3 set 0,
+//               warps 4-7 set 1; warp w owns TMEM lanes 32(w%4)..+31), epilogue
+//   warps 8-15  group 1: the same for the odd stages, so that one group's
+//               tensor-memory store latency hides behind the other's arithmetic
+//   warp  16    TMA producer (quantised tiles + token tile per stage, scales per 4)
+//   warp  17    TMEM allocation; one lane issues the MMAs and commits
 //
 // Tensor-memory columns (512 allocated): accumulators at 0 and 192 (192 fp32
 // columns each), two A staging slots of 2 x 32 columns at 384..511.
@@ -31,7 +33,8 @@
 namespace b200moe {
 namespace {
 
-constexpr int TC_THREADS = 320;
+constexpr int TC_DQ_WARPS = 16;      // two groups of 8: group g dequantises stages of parity g
+constexpr int TC_THREADS = (TC_DQ_WARPS + 2) * 32;
 constexpr int TC_KT = 64;          // k per stage
 constexpr int TC_ROWS = 128;       // weight rows per set
 constexpr int TC_NTOK = 192;       // token rows of the staged tile / accumulator columns
@@ -40,7 +43,11 @@ constexpr int TC_WSET = TC_ROWS * TC_KT;        // quantised bytes per set per s
 constexpr int TC_XTILE = TC_NTOK * TC_KT * 2;   // token tile bytes per stage
 constexpr int TC_STAGE = 2 * TC_WSET + TC_XTILE;
 constexpr int TC_STAGES = 5;
-constexpr int TC_SMEM = 1024 + TC_STAGES * TC_STAGE + 256;
+constexpr int TC_SGROUP = 4;                     // stages covered by one scale tile (256 k)
+constexpr int TC_SSLOTS = 3;                     // scale ring depth
+constexpr int TC_SSET = TC_ROWS * 16;            // 8 fp16 scales per row per group
+constexpr int TC_STILE = 2 * TC_SSET;
+constexpr int TC_SMEM = 1024 + TC_STAGES * TC_STAGE + TC_SSLOTS * TC_STILE + 256;
 constexpr uint32_t TC_COL_ACC0 = 0, TC_COL_ACC1 = 192, TC_COL_A = 384;
 static_assert(TC_STAGE % 1024 == 0, "stage alignment");
 static_assert(TC_SMEM <= 232448, "shared memory budget");
@@ -52,8 +59,6 @@ struct TcArgs {
   int tok_tile;    // upper bound on tokens per tile (multiple of 16, <= 192)
   int P;
   int act;
-  const __half* d0;  // block scales of set 0's matrix  [E*N, K/32]
-  const __half* d1;  // block scales of set 1's matrix (gate/up: the up matrix)
   void* out;
   int32_t* status;
 };
@@ -139,6 +144,7 @@ __device__ __forceinline__ uint32_t make_idesc(int m, int n) {
 template <int NMAT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
+               const __grid_constant__ CUtensorMap tm_s0, const __grid_constant__ CUtensorMap tm_s1,
                const __grid_constant__ CUtensorMap tm_x, const TcArgs args) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_seg[TC_MAX_E + 1];
@@ -147,13 +153,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   __shared__ uint32_t s_tmem;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + TC_STAGES * TC_STAGE;
+  const uint32_t scale_base = smem_base + TC_STAGES * TC_STAGE;
+  const uint32_t bar_base = scale_base + TC_SSLOTS * TC_STILE;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (TC_STAGES + s); };
   auto a_ready_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + s); };
   auto a_free_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + 2 + s); };
   const uint32_t acc_full_bar = bar_base + 8u * (2 * TC_STAGES + 4);
   const uint32_t acc_empty_bar = bar_base + 8u * (2 * TC_STAGES + 5);
+  auto sfull_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + 6 + s); };
+  auto sempty_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + 6 + TC_SSLOTS + s); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
@@ -167,7 +176,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       mbar_init(a_free_bar(s), 1);
     }
     mbar_init(acc_full_bar, 1);
-    mbar_init(acc_empty_bar, 256);
+    mbar_init(acc_empty_bar, TC_DQ_WARPS * 32);
+    for (int s = 0; s < TC_SSLOTS; ++s) {
+      mbar_init(sfull_bar(s), 1);
+      mbar_init(sempty_bar(s), TC_DQ_WARPS);
+    }
     fence_mbar_init();
     int run = 0;
     for (int e = 0; e < args.E; ++e) {
@@ -179,7 +192,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     s_seg[args.E] = args.seg[args.E];
     s_prefix[args.E] = run;
   }
-  if (warp == 9) {
+  if (warp == TC_DQ_WARPS + 1) {
     tmem_alloc(smem_u32(&s_tmem), 512);
     tmem_relinquish();
   }
@@ -207,7 +220,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     ncols = (max(rows, 1) + 15) & ~15;
   };
 
-  if (warp == 8) {
+  if (warp == TC_DQ_WARPS) {
     // ---------------------------------------------------------- TMA producer
     if (lane == 0) {
       uint32_t n = 0;
@@ -224,17 +237,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           const uint32_t fb = full_bar(slot);
           mbar_expect_tx(fb, TC_STAGE);
           const int k0 = st * TC_KT;
+          if (st % TC_SGROUP == 0) {
+            // block scales of the next 256 k for both row sets
+            const uint32_t g = n / TC_SGROUP;
+            const int ss = g % TC_SSLOTS;
+            if (!mbar_wait(sempty_bar(ss), ((g / TC_SSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+            const uint32_t sdst = scale_base + ss * TC_STILE;
+            mbar_expect_tx(sfull_bar(ss), TC_STILE);
+            tma_load_2d(sdst, &tm_s0, (k0 / 32) * 2, grow0, sfull_bar(ss));
+            tma_load_2d(sdst + TC_SSET, NMAT == 2 ? &tm_s1 : &tm_s0, (k0 / 32) * 2,
+                        NMAT == 2 ? grow0 : grow0 + TC_ROWS, sfull_bar(ss));
+          }
           tma_load_2d(sb, &tm_w0, k0, grow0, fb);
           tma_load_2d(sb + TC_WSET, NMAT == 2 ? &tm_w1 : &tm_w0, k0,
                       NMAT == 2 ? grow0 : grow0 + TC_ROWS, fb);
           tma_load_2d(sb + 2 * TC_WSET, &tm_x, k0 * 2, row0, fb);
         }
       }
+      // do not leave while copies may still land in this CTA's shared memory
       const uint32_t first = n > (uint32_t)TC_STAGES ? n - TC_STAGES : 0;
       for (uint32_t i = first; i < n; ++i)
         mbar_wait(full_bar(i % TC_STAGES), (i / TC_STAGES) & 1u, abort_flag, args.status);
+      const uint32_t groups = (n + TC_SGROUP - 1) / TC_SGROUP;
+      const uint32_t gfirst = groups > (uint32_t)TC_SSLOTS ? groups - TC_SSLOTS : 0;
+      for (uint32_t g = gfirst; g < groups; ++g)
+        mbar_wait(sfull_bar(g % TC_SSLOTS), (g / TC_SSLOTS) & 1u, abort_flag, args.status);
     }
-  } else if (warp == 9) {
+  } else if (warp == TC_DQ_WARPS + 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       uint32_t n = 0, ti = 0;
@@ -272,28 +301,28 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     }
   } else {
     // ------------------------------------- dequantise (both sets) + epilogue
-    const int set = warp >> 2;              // 0: warps 0-3, 1: warps 4-7
+    const int grp = warp >> 3;              // stage parity this warp works on
+    const int set = (warp >> 2) & 1;        // row set: 0 or 1
     const int wq = warp & 3;                // TMEM lane quarter
     const int row = wq * 32 + lane;         // weight row within the set = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
     const int sw = (row >> 1) & 3;          // 64-byte swizzle term of this row
-    const __half* dbase = (NMAT == 2 && set == 1) ? args.d1 : args.d0;
-    const int kblocks = args.K / 32;
     uint32_t n = 0, ti = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
       int e, nt, row0, rows, ncols;
       decode(tile, e, nt, row0, rows, ncols);
-      const int grow = e * args.N + nt * (NMAT == 2 ? TC_ROWS : 2 * TC_ROWS) +
-                       (NMAT == 2 ? 0 : set * TC_ROWS) + row;
-      const uint4* srow = reinterpret_cast<const uint4*>(dbase + static_cast<size_t>(grow) * kblocks);
-      uint4 sc_next = srow[0];
-      for (int sg = 0; sg < stages_per_tile / 4 && ok; ++sg) {
-        const uint4 sc4 = sc_next;
-        if (sg + 1 < stages_per_tile / 4) sc_next = srow[sg + 1];
-        const uint32_t scw[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+      for (int sg = 0; sg < stages_per_tile / TC_SGROUP && ok; ++sg) {
+        const uint32_t g = n / TC_SGROUP;
+        const int ss = g % TC_SSLOTS;
+        if (!mbar_wait(sfull_bar(ss), (g / TC_SSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
+        uint32_t scw[4];
+        lds128(scale_base + ss * TC_STILE + set * TC_SSET + row * 16, scw);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sempty_bar(ss));
 #pragma unroll
         for (int s4 = 0; s4 < 4; ++s4, ++n) {
+          if ((s4 & 1) != grp) continue;
           const int slot = n % TC_STAGES;
           const int as = n & 1;
           if (!mbar_wait(full_bar(slot), (n / TC_STAGES) & 1u, abort_flag, args.status)) { ok = false; break; }
@@ -320,11 +349,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         }
       }
       if (!ok) break;
-      // ---- epilogue: this warpgroup takes every other 16-token column chunk
+      // ---- epilogue: each of the four warpgroups takes every fourth 16-token column chunk
       if (!mbar_wait(acc_full_bar, ti & 1u, abort_flag, args.status)) break;
       tc_fence_after();
       const int seg_end = row0 + rows;
-      for (int c0 = set * 16; c0 < ncols; c0 += 32) {
+      for (int c0 = (grp * 2 + set) * 16; c0 < ncols; c0 += 64) {
         uint32_t g[16], u[16];
         tmem_ld16(tmem + lane_addr + TC_COL_ACC0 + c0, g);
         tmem_ld16(tmem + lane_addr + TC_COL_ACC1 + c0, u);
@@ -354,7 +383,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   // ---- teardown: everyone is done with tensor memory before it is freed
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == TC_DQ_WARPS + 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -370,7 +399,7 @@ int tc_launch(const CUtensorMap* maps, const TcArgs& a, cudaStream_t st) {
     B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
     configured[dev] = true;
   }
-  kern<<<sm_count(), TC_THREADS, TC_SMEM, st>>>(maps[0], maps[1], maps[2], a);
+  kern<<<sm_count(), TC_THREADS, TC_SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], a);
   B200_CHECK_CUDA(cudaGetLastError());
   return B200MOE_OK;
 }
@@ -387,10 +416,12 @@ int tc_check(const b200moe_weight_t* w, const char* name) {
   return B200MOE_OK;
 }
 
-int tc_weight_map(const b200moe_weight_t* w, CUtensorMap* tw) {
-  // 64-byte wide boxes of int8 with the 64-byte swizzle: 128 rows x 64 k
+int tc_weight_map(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts) {
+  // 64-byte wide boxes of int8 with the 64-byte swizzle: 128 rows x 64 k;
+  // scale boxes of 8 fp16 (256 k) x 128 rows, unswizzled
   const uint64_t rows = static_cast<uint64_t>(w->experts) * w->rows;
-  return make_tmap_2d_sw(tw, w->qs, rows, w->cols, TC_ROWS, 64, 64);
+  if (int rc = make_tmap_2d_sw(tw, w->qs, rows, w->cols, TC_ROWS, 64, 64)) return rc;
+  return make_tmap_2d_sw(ts, w->d, rows, static_cast<uint64_t>(w->cols) / 32 * 2, TC_ROWS, 16, 0);
 }
 
 }  // namespace
@@ -408,15 +439,14 @@ int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_til
                "tensor kernel: gate and up shapes differ");
   B200_REQUIRE(gate->rows % TC_ROWS == 0, "tensor kernel: ffn (%d) must be a multiple of 128", gate->rows);
   if (pairs == 0) return B200MOE_OK;
-  CUtensorMap maps[3];
-  if (int rc = tc_weight_map(gate, &maps[0])) return rc;
-  if (int rc = tc_weight_map(up, &maps[1])) return rc;
-  if (int rc = make_tmap_2d_sw(&maps[2], xs, pairs, static_cast<uint64_t>(gate->cols) * 2, TC_NTOK, 128, 128))
+  CUtensorMap maps[5];
+  if (int rc = tc_weight_map(gate, &maps[0], &maps[2])) return rc;
+  if (int rc = tc_weight_map(up, &maps[1], &maps[3])) return rc;
+  if (int rc = make_tmap_2d_sw(&maps[4], xs, pairs, static_cast<uint64_t>(gate->cols) * 2, TC_NTOK, 128, 128))
     return rc;
   TcArgs a{};
   a.seg = seg; a.E = gate->experts; a.N = gate->rows; a.K = gate->cols;
   a.ntiles = gate->rows / TC_ROWS; a.tok_tile = tok_tile; a.P = pairs; a.act = act;
-  a.d0 = static_cast<const __half*>(gate->d); a.d1 = static_cast<const __half*>(up->d);
   a.out = a_out; a.status = device_status_ptr();
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
   return tc_launch<2>(maps, a, st);
@@ -428,15 +458,15 @@ int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile
   B200_REQUIRE(down->rows % (2 * TC_ROWS) == 0, "tensor kernel: hidden (%d) must be a multiple of 256",
                down->rows);
   if (pairs == 0) return B200MOE_OK;
-  CUtensorMap maps[3];
-  if (int rc = tc_weight_map(down, &maps[0])) return rc;
+  CUtensorMap maps[5];
+  if (int rc = tc_weight_map(down, &maps[0], &maps[2])) return rc;
   maps[1] = maps[0];
-  if (int rc = make_tmap_2d_sw(&maps[2], a_in, pairs, static_cast<uint64_t>(down->cols) * 2, TC_NTOK, 128, 128))
+  maps[3] = maps[2];
+  if (int rc = make_tmap_2d_sw(&maps[4], a_in, pairs, static_cast<uint64_t>(down->cols) * 2, TC_NTOK, 128, 128))
     return rc;
   TcArgs a{};
   a.seg = seg; a.E = down->experts; a.N = down->rows; a.K = down->cols;
   a.ntiles = down->rows / (2 * TC_ROWS); a.tok_tile = tok_tile; a.P = pairs; a.act = 0;
-  a.d0 = static_cast<const __half*>(down->d); a.d1 = a.d0;
   a.out = d_out; a.status = device_status_ptr();
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
   return tc_launch<1>(maps, a, st);
