@@ -218,6 +218,8 @@ def main():
     if rank == 0:
         sampler.start()
     C.check(C.lib.b200moe_profile_enable(1))
+    if world > 1:
+        block.backend.profile = True
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record()
@@ -230,6 +232,8 @@ def main():
     calls = ctypes.c_int32(0)
     C.check(C.lib.b200moe_profile_read(stage_ms, ctypes.byref(calls)))
     C.check(C.lib.b200moe_profile_enable(0))
+    if world > 1:
+        block.backend.profile = False
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([ms_total], device=dev)
@@ -269,7 +273,28 @@ def main():
         e2e = {"value": tokens * args.steps / dt, "unit": "tokens/s",
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
     else:
-        e2e = block.e2e(h, args.steps)
+        hp = h.cpu().pin_memory()
+        yp = torch.empty_like(hp).pin_memory()
+        h_dev = torch.empty_like(h)
+        nbytes = hp.numel() * hp.element_size()
+
+        def e2e_step():
+            h_dev.copy_(hp, non_blocking=True)
+            yy = block(h_dev)
+            yp.copy_(yy, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        barrier()
+        dt = torch.tensor([time.perf_counter() - t0], device=dev)
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {"value": tokens * args.steps / float(dt.item()), "unit": "tokens/s",
+               "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": nbytes * world}
 
     # ---- roofline of the dominant kernel (gate/up), from the stage events
     n_calls = max(int(calls.value), 1)
@@ -294,7 +319,23 @@ def main():
         whole = {"tensor_frac": flops / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
                  "hbm_frac": layer_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     else:
-        roofline, whole = block.roofline(stage, peaks, tokens), None
+        # gate/up kernel on every rank: flops of the rows each rank received over
+        # the slowest rank's mean kernel time, against N x the single-GPU peak
+        tm = block.backend.timings
+        gu_ms = sum(ev[0].elapsed_time(ev[1]) for ev, _ in tm) / max(len(tm), 1)
+        rows = sum(n for _, n in tm) / max(len(tm), 1)
+        t = torch.tensor([gu_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        r = torch.tensor([rows], device=dev)
+        dist.all_reduce(r, op=dist.ReduceOp.SUM)
+        gu_flops = float(r.item()) * 2 * 2 * spec.ffn * spec.hidden
+        ach = gu_flops / (float(t.item()) * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"] * world
+        roofline = {"bound": "tensor", "kernel": "gate_up", "achieved": ach, "peak": peak,
+                    "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                    "peak_source": peaks["source"] + f" (cuBLAS bf16 burst x {world} GPUs)"}
+        stage = {"gate_up_max_over_ranks": float(t.item())}
+        whole = {"tensor_frac": flops / (ms_step * 1e-3) / 1e12 / peak}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -1,0 +1,61 @@
+"""Expert parallelism on real GPUs: two processes, two GPUs, NCCL all-to-all.
+Skipped on a single-GPU machine (the CPU suite covers the protocol under gloo)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import moe_oracle as orc
+from shark_platform_b200 import synthetic as syn
+from helpers import oracle_params
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, name, tokens, regime, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from shark_platform_b200 import moe, parallel
+
+        spec = syn.CASES[name]
+        case = syn.make_case(spec, tokens=tokens)
+        block = parallel.build_from_case(case, regime=regime)
+        per = tokens // world
+        full = case.h.reshape(tokens, spec.hidden)
+        lo, hi = rank * per, (tokens if rank == world - 1 else (rank + 1) * per)
+        h = full[lo:hi].cuda()
+        if spec.act_dtype == "bf16":
+            h = h.to(torch.bfloat16)
+        y = block(h).float().cpu()
+        torch.cuda.synchronize()
+        assert moe.device_status() == 0
+        want, _ = orc.moe_block(case.h, oracle_params(case), form="per_expert")
+        out[rank] = orc.rel_l2(y, want.reshape(tokens, spec.hidden)[lo:hi])
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name,tokens,regime", [("small_q8", 40, "auto"), ("small_q4k", 33, "auto"),
+                                                ("small_grok", 300, "tensor")])
+def test_expert_parallel_two_gpus(name, tokens, regime):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(world, _free_port(), name, tokens, regime, out), nprocs=world, join=True)
+        for r in range(world):
+            assert out[r] < 2e-2, (r, out[r])
