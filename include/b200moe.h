@@ -177,13 +177,27 @@ int b200moe_down_noalloc(const void* a, const int32_t* seg_offsets, int32_t pair
 /* y[t] = h[t] + norm?( sum_slot gates[t,slot] * D[inv[t*k+slot]] ): the
  * "me,men->men" scaling and torch.sum over slots (layers/ffn_moe_block.py:
  * 73-74), the optional layer_output_norm and the residual
- * (layers/mixture_of_experts_block.py:86-90).  Pairs with inv < 0 (experts of
- * another rank) contribute nothing.  If add_residual is 0 the result is the
- * un-normalised partial sum (used under expert parallelism). */
-int b200moe_combine(const float* d_partials, int32_t ksplit, int32_t pairs, const int32_t* inv,
-                    const float* gates, const void* h, int h_dtype, int32_t tokens,
-                    const b200moe_layer_t* layer, int add_residual, void* y_out, int y_dtype,
-                    void* stream);
+ * (layers/mixture_of_experts_block.py:86-90).  d_partials: [ksplit, pairs, d]
+ * of d_dtype (F32, or BF16 for rows that came back from another rank).  Pairs
+ * with inv < 0 contribute nothing.  If add_residual is 0 the result is the
+ * un-normalised weighted sum. */
+int b200moe_combine(const void* d_partials, int d_dtype, int32_t ksplit, int32_t pairs,
+                    const int32_t* inv, const float* gates, const void* h, int h_dtype,
+                    int32_t tokens, const b200moe_layer_t* layer, int add_residual, void* y_out,
+                    int y_dtype, void* stream);
+
+/* Expert parallelism (no reference counterpart: the reference holds all shards
+ * in one process, ops/sharded_impls.py).  Rows arriving from `world` source
+ * ranks, each source's rows ordered by local expert, are regrouped per expert:
+ * counts[s*experts_local + e] = rows from source s for local expert e;
+ * seg_offsets [experts_local+1]; perm [rows] (grouped position -> arrival
+ * position); inv [rows] (arrival position -> grouped position). */
+int b200moe_exchange_plan(const int32_t* counts, int32_t world, int32_t experts_local,
+                          int32_t* seg_offsets, int32_t* perm, int32_t* inv, void* stream);
+
+/* out[i,:] = rows[idx[i] / div,:] for i < n; row_bytes a multiple of 16. */
+int b200moe_gather_rows(const void* rows, const int32_t* idx, int32_t n, int32_t div,
+                        int32_t row_bytes, void* out, void* stream);
 
 /* Bytes of workspace b200moe_layer_forward needs for up to `tokens` tokens. */
 size_t b200moe_workspace_bytes(const b200moe_layer_t* layer, int32_t tokens);

@@ -91,7 +91,9 @@ _PROTOS = {
     "b200moe_down_ksplit": (c_int, [_W, c_int32, c_int32, c_int]),
     "b200moe_down": (c_int, [_P, _P, c_int32, c_int32, _W, c_int, _P, _P]),
     "b200moe_down_noalloc": (c_int, [_P, _P, c_int32, c_int32, _W, _P, _P]),
-    "b200moe_combine": (c_int, [_P, c_int32, c_int32, _P, _P, _P, c_int, c_int32, _L, c_int, _P, c_int, _P]),
+    "b200moe_combine": (c_int, [_P, c_int, c_int32, c_int32, _P, _P, _P, c_int, c_int32, _L, c_int, _P, c_int, _P]),
+    "b200moe_exchange_plan": (c_int, [_P, c_int32, c_int32, _P, _P, _P, _P]),
+    "b200moe_gather_rows": (c_int, [_P, _P, c_int32, c_int32, c_int32, _P, _P]),
     "b200moe_workspace_bytes": (c_size_t, [_L, c_int32]),
     "b200moe_layer_forward": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, c_size_t, _P, _P, _P]),
     "b200moe_layer_forward_host": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, _P, c_size_t, _P]),

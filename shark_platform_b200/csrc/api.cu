@@ -332,14 +332,27 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
                             static_cast<cudaStream_t>(stream));
 }
 
-int b200moe_combine(const float* d_partials, int32_t ksplit, int32_t pairs, const int32_t* inv,
+int b200moe_exchange_plan(const int32_t* counts, int32_t world, int32_t experts_local,
+                          int32_t* seg_offsets, int32_t* perm, int32_t* inv, void* stream) {
+  B200_REQUIRE(counts && seg_offsets && perm && inv, "exchange_plan: NULL argument");
+  return launch_exchange_plan(counts, world, experts_local, seg_offsets, perm, inv,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_gather_rows(const void* rows, const int32_t* idx, int32_t n, int32_t div,
+                        int32_t row_bytes, void* out, void* stream) {
+  B200_REQUIRE(n >= 0 && (n == 0 || (rows && idx && out)), "gather_rows: bad argument");
+  return launch_gather_rows(rows, idx, n, div, row_bytes, out, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_combine(const void* d_partials, int d_dtype, int32_t ksplit, int32_t pairs, const int32_t* inv,
                     const float* gates, const void* h, int h_dtype, int32_t tokens,
                     const b200moe_layer_t* layer, int add_residual, void* y_out, int y_dtype,
                     void* stream) {
   B200_REQUIRE(layer && ksplit >= 1, "combine: bad argument");
   B200_REQUIRE(tokens == 0 || (d_partials && inv && gates && y_out), "combine: NULL buffer");
   B200_REQUIRE(!add_residual || h, "combine: residual requested without h");
-  return launch_combine(d_partials, ksplit, pairs, inv, gates, h, h_dtype, tokens, layer,
+  return launch_combine(d_partials, d_dtype, ksplit, pairs, inv, gates, h, h_dtype, tokens, layer,
                         add_residual, y_out, y_dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -386,8 +399,8 @@ int b200moe_layer_forward(const b200moe_layer_t* L, const void* h, void* y, int 
   const int ks = b200moe_down_ksplit(&L->down, pairs, tokens, regime);
   if (int rc = b200moe_down(w.a, w.seg, pairs, tokens, &L->down, regime, w.dpart, stream)) return rc;
   prof_mark(pc, 5, st);
-  if (int rc = launch_combine(w.dpart, ks, pairs, w.inv, w.gates, h, io_dtype, tokens, L, 1, y,
-                              io_dtype, st))
+  if (int rc = launch_combine(w.dpart, B200MOE_DT_F32, ks, pairs, w.inv, w.gates, h, io_dtype,
+                              tokens, L, 1, y, io_dtype, st))
     return rc;
   prof_mark(pc, 6, st);
   if (experts_out)

@@ -10,7 +10,11 @@ int launch_route_plan(const int32_t* experts, int pairs, int e_begin, int E, int
                       int32_t* seg, int32_t* perm, int32_t* inv, cudaStream_t st);
 int launch_permute_rows(const void* xn, const int32_t* perm, const int32_t* seg, int E, int pairs,
                         int k, int d, int kperm, void* xs, cudaStream_t st);
-int launch_combine(const float* dpart, int ksplit, int pairs, const int32_t* inv,
+int launch_exchange_plan(const int32_t* counts, int world, int el, int32_t* seg, int32_t* perm,
+                         int32_t* inv, cudaStream_t st);
+int launch_gather_rows(const void* rows, const int32_t* idx, int n, int div, int row_bytes,
+                       void* out, cudaStream_t st);
+int launch_combine(const void* dpart, int d_dtype, int ksplit, int pairs, const int32_t* inv,
                    const float* gates, const void* h, int h_dtype, int tokens,
                    const b200moe_layer_t* L, int add_residual, void* y, int y_dtype,
                    cudaStream_t st);

@@ -143,6 +143,148 @@ router_kernel(const T* __restrict__ h, int tokens, int d, int E, int k, float ep
   }
 }
 
+// Softmax over the logits of one token held in shared memory, top-k and gate
+// renormalisation by one warp (shared by both router kernels).
+__device__ __forceinline__ void router_select(const float* logit, int lane, int E, int k,
+                                              int32_t* experts_out, float* gates_out) {
+  const float NEG = -INFINITY;
+  float l0 = lane < E ? logit[lane] : NEG;
+  float l1 = lane + 32 < E ? logit[lane + 32] : NEG;
+  float mx = fmaxf(l0, l1);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float p0 = lane < E ? expf(l0 - mx) : 0.f;
+  float p1 = lane + 32 < E ? expf(l1 - mx) : 0.f;
+  float sum = p0 + p1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  p0 = lane < E ? p0 / sum : -1.f;
+  p1 = lane + 32 < E ? p1 / sum : -1.f;
+  float sel_p[MAX_TOPK];
+  int sel_i[MAX_TOPK];
+  float gsum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_TOPK; ++i) {
+    if (i < k) {
+      float bp = p0;
+      int bi = lane;
+      if (p1 > bp) { bp = p1; bi = lane + 32; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float op = __shfl_xor_sync(0xffffffffu, bp, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (op > bp || (op == bp && oi < bi)) { bp = op; bi = oi; }
+      }
+      sel_p[i] = bp;
+      sel_i[i] = bi;
+      gsum += bp;
+      if (bi == lane) p0 = -1.f;
+      if (bi == lane + 32) p1 = -1.f;
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < MAX_TOPK; ++i) {
+      if (i < k) {
+        experts_out[i] = sel_i[i];
+        gates_out[i] = sel_p[i] / gsum;
+      }
+    }
+  }
+}
+
+// One CTA per token: used for small token counts (decode), where a warp per
+// token leaves most of the GPU idle.  The row stays in registers between the
+// two passes (hidden <= 8192).
+constexpr int RB_THREADS = 256;
+constexpr int RB_MAXV = 4;  // 8-element vectors per thread
+
+template <typename T>
+__global__ void __launch_bounds__(RB_THREADS)
+router_block_kernel(const T* __restrict__ h, int d, int E, int k, float eps,
+                    const float* __restrict__ norm_w, const float* __restrict__ rw,
+                    const float* __restrict__ rb, __half* __restrict__ xn_out,
+                    int32_t* __restrict__ experts_out, float* __restrict__ gates_out) {
+  __shared__ float s_part[RB_THREADS / 32][8];
+  __shared__ float s_logit[MAX_EXPERTS];
+  __shared__ float s_ss[RB_THREADS / 32];
+  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const T* row = h + static_cast<size_t>(t) * d;
+  const int nvec = d / 8;
+  float x[RB_MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < RB_MAXV; ++v) {
+    const int j = tid + v * RB_THREADS;
+    if (j < nvec) {
+      load8<T>(row + j * 8, x[v]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(x[v][i], x[v][i], ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) s_ss[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < RB_THREADS / 32; ++w) tot += s_ss[w];
+  const float rstd = 1.0f / sqrtf(tot / static_cast<float>(d) + eps);
+#pragma unroll
+  for (int v = 0; v < RB_MAXV; ++v) {
+    const int j = tid + v * RB_THREADS;
+    if (j < nvec) {
+      float w[8];
+      load8<float>(norm_w + j * 8, w);
+      uint32_t packed[4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[v][i] = w[i] * (x[v][i] * rstd);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        packed[i] = h2_as_u32(__halves2half2(to_half_sat(x[v][2 * i]), to_half_sat(x[v][2 * i + 1])));
+      *reinterpret_cast<uint4*>(xn_out + static_cast<size_t>(t) * d + j * 8) =
+          make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+  }
+  for (int e0 = 0; e0 < E; e0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int v = 0; v < RB_MAXV; ++v) {
+      const int j = tid + v * RB_THREADS;
+      if (j < nvec) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (e0 + e < E) {
+            float r[8];
+            load8<float>(rw + static_cast<size_t>(e0 + e) * d + j * 8, r);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[e] = fmaf(x[v][i], r[i], acc[e]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+      if (lane == 0) s_part[warp][e] = acc[e];
+    }
+    __syncthreads();
+    if (tid < 8 && e0 + tid < E) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < RB_THREADS / 32; ++w) v += s_part[w][tid];
+      s_logit[e0 + tid] = v + (rb ? rb[e0 + tid] : 0.f);
+    }
+    __syncthreads();
+  }
+  if (warp == 0)
+    router_select(s_logit, lane, E, k, experts_out + static_cast<size_t>(t) * k,
+                  gates_out + static_cast<size_t>(t) * k);
+}
+
 int launch_router(const void* h, int h_dtype, int tokens, const b200moe_layer_t* L, void* xn,
                   int32_t* experts, float* gates, cudaStream_t st) {
   B200_REQUIRE(L->hidden % 256 == 0, "router: hidden (%d) must be a multiple of 256", L->hidden);
@@ -151,6 +293,22 @@ int launch_router(const void* h, int h_dtype, int tokens, const b200moe_layer_t*
   B200_REQUIRE(L->top_k >= 1 && L->top_k <= MAX_TOPK && L->top_k <= L->experts,
                "router: top_k (%d) must be 1..min(8, experts)", L->top_k);
   if (tokens == 0) return B200MOE_OK;
+  B200_REQUIRE(h_dtype == B200MOE_DT_F32 || h_dtype == B200MOE_DT_BF16,
+               "router: activations must be fp32 or bf16");
+  if (tokens <= 512 && L->hidden <= 8 * RB_THREADS * RB_MAXV) {
+    if (h_dtype == B200MOE_DT_F32)
+      router_block_kernel<float><<<tokens, RB_THREADS, 0, st>>>(
+          static_cast<const float*>(h), L->hidden, L->experts, L->top_k, L->rms_epsilon,
+          L->ffn_norm_weight, L->router_weight, L->router_bias, static_cast<__half*>(xn), experts,
+          gates);
+    else
+      router_block_kernel<__nv_bfloat16><<<tokens, RB_THREADS, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(h), L->hidden, L->experts, L->top_k, L->rms_epsilon,
+          L->ffn_norm_weight, L->router_weight, L->router_bias, static_cast<__half*>(xn), experts,
+          gates);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return B200MOE_OK;
+  }
   dim3 grid((tokens + ROUTER_WARPS - 1) / ROUTER_WARPS), block(ROUTER_WARPS * 32);
   if (h_dtype == B200MOE_DT_F32) {
     router_kernel<float><<<grid, block, 0, st>>>(
@@ -283,6 +441,67 @@ int launch_permute_rows(const void* xn, const int32_t* perm, const int32_t* seg,
   return B200MOE_OK;
 }
 
+// --------------------------------------------------- exchange plan (EP)
+// Rows arrive from `world` source ranks, each rank's rows ordered by local
+// expert: arrival order is (source, expert) blocks, the kernels want (expert,
+// source) blocks.  counts[s*el + e] = rows from source s for local expert e.
+// One CTA computes the segment offsets and both permutations.
+__global__ void __launch_bounds__(1024)
+exchange_plan_kernel(const int32_t* __restrict__ counts, int world, int el,
+                     int32_t* __restrict__ seg, int32_t* __restrict__ perm,
+                     int32_t* __restrict__ inv) {
+  __shared__ int s_arr[MAX_EXPERTS * MAX_EXPERTS];  // arrival offset of block (s, e)
+  __shared__ int s_srt[MAX_EXPERTS * MAX_EXPERTS];  // sorted offset of block (s, e)
+  const int nb = world * el;
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int b = 0; b < nb; ++b) { s_arr[b] = run; run += counts[b]; }
+    run = 0;
+    for (int e = 0; e < el; ++e) {
+      seg[e] = run;
+      for (int s = 0; s < world; ++s) { s_srt[s * el + e] = run; run += counts[s * el + e]; }
+    }
+    seg[el] = run;
+  }
+  __syncthreads();
+  for (int b = 0; b < nb; ++b) {
+    const int c = counts[b], a0 = s_arr[b], p0 = s_srt[b];
+    for (int i = threadIdx.x; i < c; i += blockDim.x) {
+      perm[p0 + i] = a0 + i;
+      inv[a0 + i] = p0 + i;
+    }
+  }
+}
+
+int launch_exchange_plan(const int32_t* counts, int world, int el, int32_t* seg, int32_t* perm,
+                         int32_t* inv, cudaStream_t st) {
+  B200_REQUIRE(world >= 1 && el >= 1 && world * el <= MAX_EXPERTS * MAX_EXPERTS && el <= MAX_EXPERTS,
+               "exchange_plan: %d ranks x %d local experts out of range", world, el);
+  exchange_plan_kernel<<<1, 1024, 0, st>>>(counts, world, el, seg, perm, inv);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+// out[i,:] = rows[idx[i] / div,:] for i < n; rows of `vec_per_row` 16-byte vectors.
+__global__ void __launch_bounds__(128)
+gather_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ idx, int div,
+                   int vec_per_row, uint4* __restrict__ out) {
+  const int i = blockIdx.x;
+  const uint4* src = rows + static_cast<size_t>(idx[i] / div) * vec_per_row;
+  uint4* dst = out + static_cast<size_t>(i) * vec_per_row;
+  for (int j = threadIdx.x; j < vec_per_row; j += blockDim.x) dst[j] = src[j];
+}
+
+int launch_gather_rows(const void* rows, const int32_t* idx, int n, int div, int row_bytes,
+                       void* out, cudaStream_t st) {
+  B200_REQUIRE(row_bytes % 16 == 0 && div >= 1, "gather_rows: rows must be multiples of 16 bytes");
+  if (n == 0) return B200MOE_OK;
+  gather_rows_kernel<<<n, 128, 0, st>>>(static_cast<const uint4*>(rows), idx, div, row_bytes / 16,
+                                        static_cast<uint4*>(out));
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
 // ----------------------------------------------------------------- combine
 // One CTA per token: sum over slots (in slot order) of gate * (sum of the
 // k-split partials of the pair's down-projection row), optional output RMS
@@ -306,15 +525,34 @@ __device__ __forceinline__ void store1<__nv_bfloat16>(__nv_bfloat16* p, float v)
 
 constexpr int COMBINE_THREADS = 256;
 
-template <typename TH, typename TY>
+template <typename TD, typename TH, typename TY>
 __global__ void __launch_bounds__(COMBINE_THREADS)
-combine_kernel(const float* __restrict__ dpart, int ksplit, size_t part_stride,
+combine_kernel(const TD* __restrict__ dpart, int ksplit, size_t part_stride,
                const int32_t* __restrict__ inv, const float* __restrict__ gates,
                const TH* __restrict__ h, int d, int k, const float* __restrict__ out_norm_w,
                float eps, int add_residual, TY* __restrict__ y) {
   extern __shared__ float s_row[];
   __shared__ float s_red[COMBINE_THREADS / 32];
   const int t = blockIdx.x;
+  if (gridDim.y > 1) {
+    // no output norm: column slices are independent, one slice per blockIdx.y
+    const int per = (d + gridDim.y - 1) / gridDim.y;
+    const int j0 = blockIdx.y * per, j1 = min(d, j0 + per);
+    for (int j = j0 + threadIdx.x; j < j1; j += COMBINE_THREADS) {
+      float acc = 0.f;
+      for (int s = 0; s < k; ++s) {
+        const int pos = inv[static_cast<size_t>(t) * k + s];
+        if (pos < 0) continue;
+        float v = 0.f;
+        for (int c = 0; c < ksplit; ++c)
+          v += load1<TD>(dpart + c * part_stride + static_cast<size_t>(pos) * d + j);
+        acc += gates[static_cast<size_t>(t) * k + s] * v;
+      }
+      if (add_residual) acc += load1<TH>(h + static_cast<size_t>(t) * d + j);
+      store1<TY>(y + static_cast<size_t>(t) * d + j, acc);
+    }
+    return;
+  }
   float ss = 0.f;
   for (int j = threadIdx.x; j < d; j += COMBINE_THREADS) {
     float acc = 0.f;
@@ -323,7 +561,7 @@ combine_kernel(const float* __restrict__ dpart, int ksplit, size_t part_stride,
       if (pos < 0) continue;
       float v = 0.f;
       for (int c = 0; c < ksplit; ++c)
-        v += dpart[c * part_stride + static_cast<size_t>(pos) * d + j];
+        v += load1<TD>(dpart + c * part_stride + static_cast<size_t>(pos) * d + j);
       acc += gates[static_cast<size_t>(t) * k + s] * v;
     }
     s_row[j] = acc;
@@ -349,7 +587,7 @@ combine_kernel(const float* __restrict__ dpart, int ksplit, size_t part_stride,
   }
 }
 
-int launch_combine(const float* dpart, int ksplit, int pairs, const int32_t* inv,
+int launch_combine(const void* dpart, int d_dtype, int ksplit, int pairs, const int32_t* inv,
                    const float* gates, const void* h, int h_dtype, int tokens,
                    const b200moe_layer_t* L, int add_residual, void* y, int y_dtype,
                    cudaStream_t st) {
@@ -358,19 +596,25 @@ int launch_combine(const float* dpart, int ksplit, int pairs, const int32_t* inv
   const size_t smem = static_cast<size_t>(d) * sizeof(float);
   B200_REQUIRE(smem <= 48 * 1024, "combine: hidden (%d) too large", d);
   const size_t stride = static_cast<size_t>(pairs) * d;
-  dim3 grid(tokens), block(COMBINE_THREADS);
-#define LAUNCH(TH, TY)                                                                         \
-  combine_kernel<TH, TY><<<grid, block, smem, st>>>(dpart, ksplit, stride, inv, gates,         \
-                                                    static_cast<const TH*>(h), d, k,           \
-                                                    L->layer_output_norm_weight,               \
-                                                    L->rms_epsilon, add_residual,              \
-                                                    static_cast<TY*>(y))
+  const bool need_row = L->layer_output_norm_weight != nullptr && add_residual;
+  int slices = 1;
+  if (!need_row && tokens < 1024) slices = max(1, min(d / COMBINE_THREADS, 2048 / tokens));
+  dim3 grid(tokens, slices), block(COMBINE_THREADS);
+#define LAUNCH(TD, TH, TY)                                                                     \
+  combine_kernel<TD, TH, TY><<<grid, block, smem, st>>>(static_cast<const TD*>(dpart), ksplit,   \
+                                                        stride, inv, gates,                      \
+                                                        static_cast<const TH*>(h), d, k,         \
+                                                        L->layer_output_norm_weight,             \
+                                                        L->rms_epsilon, add_residual,            \
+                                                        static_cast<TY*>(y))
+  const bool dbf = d_dtype == B200MOE_DT_BF16;
+  B200_REQUIRE(dbf || d_dtype == B200MOE_DT_F32, "combine: partial rows must be fp32 or bf16");
   if (h_dtype == B200MOE_DT_F32 && y_dtype == B200MOE_DT_F32) {
-    LAUNCH(float, float);
+    if (dbf) LAUNCH(__nv_bfloat16, float, float); else LAUNCH(float, float, float);
   } else if (h_dtype == B200MOE_DT_BF16 && y_dtype == B200MOE_DT_BF16) {
-    LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    if (dbf) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16); else LAUNCH(float, __nv_bfloat16, __nv_bfloat16);
   } else if (h_dtype == B200MOE_DT_BF16 && y_dtype == B200MOE_DT_F32) {
-    LAUNCH(__nv_bfloat16, float);
+    if (dbf) LAUNCH(__nv_bfloat16, __nv_bfloat16, float); else LAUNCH(float, __nv_bfloat16, float);
   } else {
     B200_REQUIRE(false, "combine: unsupported dtype pair (%d, %d)", h_dtype, y_dtype);
   }

@@ -35,15 +35,15 @@ class Exchange:
 
     send_splits: list[int]       # rows this rank sends to each rank
     recv_splits: list[int]       # rows this rank receives from each rank
-    recv_expert: torch.Tensor    # int32 [rows received]: local expert id of each arriving row
+    recv_counts: torch.Tensor    # int32 [world, E_local] on the device: rows per (source, expert)
     max_segment: int             # most rows any local expert receives
 
 
 def plan_exchange(counts_local: torch.Tensor, world: int, group) -> Exchange:
     """counts_local: int32 [E] rows this rank routes to each *global* expert.
     One small all-to-all tells every rank how many rows arrive per (source
-    rank, local expert).  Synchronises with the host (NCCL needs host-side
-    split sizes)."""
+    rank, local expert).  Synchronises with the host once (NCCL needs
+    host-side split sizes)."""
     E = counts_local.numel()
     el = E // world
     send_counts = counts_local.reshape(world, el).contiguous()
@@ -52,10 +52,8 @@ def plan_exchange(counts_local: torch.Tensor, world: int, group) -> Exchange:
     both = torch.stack([send_counts, recv_counts]).cpu()
     send_splits = both[0].sum(dim=1).tolist()
     recv_splits = both[1].sum(dim=1).tolist()
-    ids = torch.arange(el, dtype=torch.int32, device=counts_local.device).repeat(world)
-    recv_expert = torch.repeat_interleave(ids, recv_counts.reshape(-1).to(torch.int64))
     max_segment = int(both[1].sum(dim=0).max()) if el > 0 else 0
-    return Exchange(send_splits, recv_splits, recv_expert.to(torch.int32), max_segment)
+    return Exchange(send_splits, recv_splits, recv_counts, max_segment)
 
 
 def exchange_rows(rows: torch.Tensor, send_splits, recv_splits, group) -> torch.Tensor:
@@ -71,8 +69,9 @@ class ExpertParallelMoeBlock(torch.nn.Module):
     backend methods (CUDA implementation: `CudaBackend` below):
       route(h)                         -> xn [T,d], experts int32 [T,k], gates f32 [T,k]
       plan(experts, n_experts, begin)  -> counts, seg_offsets, perm, inv
+      regroup(recv_counts, n)          -> seg_offsets, perm, inv of the arrived rows by local expert
       gather(rows, perm, top_k, n)     -> rows[perm // top_k] for the first n positions
-      expert_ffn(xs, seg, max_segment) -> f32 [rows, d]
+      expert_ffn(xs, seg, max_segment) -> [rows, d] in the wire dtype of the return trip
       combine(rows, inv, gates, h)     -> y
     """
 
@@ -99,7 +98,7 @@ class ExpertParallelMoeBlock(torch.nn.Module):
         ex = plan_exchange(counts, self.world, self.group)
         recv_rows = exchange_rows(send_rows, ex.send_splits, ex.recv_splits, self.group)
         n_recv = recv_rows.shape[0]
-        _, seg2, perm2, inv2 = b.plan(ex.recv_expert, self.experts_local, 0)
+        seg2, perm2, inv2 = b.regroup(ex.recv_counts, n_recv)
         xs = b.gather(recv_rows, perm2, 1, n_recv)
         d_sorted = b.expert_ffn(xs, seg2, max(ex.max_segment, 1))
         d_arrival = b.gather(d_sorted, inv2, 1, n_recv)
@@ -153,11 +152,20 @@ class CudaBackend:
         out = torch.empty((n,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=self.dev)
         if n == 0:
             return out
-        halves = rows.shape[1] * rows.element_size() // 2
-        seg = torch.tensor([0, n], dtype=torch.int32, device=self.dev)
-        C.check(C.lib.b200moe_permute_rows(self._p(rows), self._p(perm), self._p(seg), 1, n, top_k,
-                                           halves, 0, self._p(out), self._st()), "permute_rows")
+        C.check(C.lib.b200moe_gather_rows(self._p(rows), self._p(perm), n, top_k,
+                                          rows.shape[1] * rows.element_size(), self._p(out),
+                                          self._st()), "gather_rows")
         return out
+
+    def regroup(self, recv_counts, n):
+        C = self.C
+        world, el = recv_counts.shape
+        seg = torch.empty(el + 1, dtype=torch.int32, device=self.dev)
+        perm = torch.empty(max(n, 1), dtype=torch.int32, device=self.dev)
+        inv = torch.empty(max(n, 1), dtype=torch.int32, device=self.dev)
+        C.check(C.lib.b200moe_exchange_plan(self._p(recv_counts), world, el, self._p(seg),
+                                            self._p(perm), self._p(inv), self._st()), "exchange_plan")
+        return seg, perm[:n], inv[:n]
 
     def expert_ffn(self, xs, seg, max_segment):
         C, L = self.C, self.layer
@@ -185,7 +193,9 @@ class CudaBackend:
             ev[2].record()
             self.timings.append((ev, n))
         out = part[0] if ks == 1 else part.sum(dim=0)
-        return out[:n]
+        # result rows travel back as bf16: half the NVLink bytes, and the layer
+        # output is rounded to the activation dtype anyway
+        return out[:n].to(torch.bfloat16)
 
     def combine(self, rows, inv, gates, h):
         C, L = self.C, self.layer
@@ -194,7 +204,8 @@ class CudaBackend:
         y = torch.empty_like(h)
         dt = C.DT_F32 if h.dtype == torch.float32 else C.DT_BF16
         rows = rows.contiguous()
-        C.check(C.lib.b200moe_combine(self._p(rows), 1, rows.shape[0], self._p(inv), self._p(gates),
+        ddt = C.DT_BF16 if rows.dtype == torch.bfloat16 else C.DT_F32
+        C.check(C.lib.b200moe_combine(self._p(rows), ddt, 1, rows.shape[0], self._p(inv), self._p(gates),
                                       self._p(h), dt, tokens, ctypes.byref(L.desc), 1, self._p(y),
                                       dt, self._st()), "combine")
         return y

@@ -33,6 +33,14 @@ class OracleBackend:
         counts, seg, perm, inv = orc.route_plan(flat, n_experts)
         return counts.to(torch.int32), seg.to(torch.int32), perm.to(torch.int32), inv.to(torch.int32)
 
+    def regroup(self, recv_counts, n):
+        world, el = recv_counts.shape
+        ids = torch.arange(el).repeat(world)
+        arrival_expert = torch.repeat_interleave(ids, recv_counts.reshape(-1).to(torch.int64))
+        assert arrival_expert.numel() == n
+        _, seg, perm, inv = orc.route_plan(arrival_expert, el)
+        return seg.to(torch.int32), perm.to(torch.int32), inv.to(torch.int32)
+
     def gather(self, rows, perm, top_k, n):
         return rows[(perm[:n].to(torch.int64) // top_k)]
 
@@ -107,7 +115,7 @@ def test_plan_exchange_single_rank_is_identity():
         counts = torch.tensor([3, 0, 2, 5], dtype=torch.int32)
         ex = plan_exchange(counts, 1, dist.group.WORLD)
         assert ex.send_splits == [10] and ex.recv_splits == [10]
-        assert ex.recv_expert.tolist() == [0, 0, 0, 2, 2, 3, 3, 3, 3, 3]
+        assert ex.recv_counts.tolist() == [[3, 0, 2, 5]]
         assert ex.max_segment == 5
     finally:
         dist.destroy_process_group()
