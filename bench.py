@@ -181,9 +181,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     from shark_platform_b200 import _cabi as C, moe, synthetic as syn
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from helpers import b200_block, device_input
-
+    b200_block, device_input = syn.case_block, syn.case_input
     spec = syn.CASES[spec_name]
     case = syn.make_case(spec, tokens=tokens)
     peaks = measured_peaks()

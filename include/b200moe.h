@@ -51,7 +51,8 @@ typedef struct {
   int32_t cols;
   const void* qs;  /* quantised values (or dense fp16 values) */
   const void* d;   /* Q8_0: per-block fp16 scales; otherwise NULL */
-  const void* sub; /* Q4_K: per-sub-block (scale, min) half2 pairs; otherwise NULL */
+  const void* sub; /* Q4_K: per-sub-block (scale, min) half2 pairs (required);
+                      Q8_0: stage-tiled scales from b200moe_q8_prepare or NULL */
 } b200moe_weight_t;
 
 /* Parameters of one MoeBlock (layers/mixture_of_experts_block.py:31-62). */
@@ -92,6 +93,13 @@ int b200moe_dequant(const b200moe_weight_t* w, int out_dtype, void* out, void* s
 int b200moe_q4k_prepare(const void* d, const void* dmin, const uint8_t* sb_scales_high,
                         const uint8_t* sb_scales_low, const uint8_t* sb_mins_high,
                         const uint8_t* sb_mins_low, int64_t blocks, void* sub_out, void* stream);
+
+/* Q8_0, optional: the block scales `d` [rows, cols/32] (rows = E*N) transposed
+ * to [cols/256][rows][8] so that the scales of a 256-k stage are one contiguous
+ * run per row tile.  Pass the result as b200moe_weight_t.sub; with sub == NULL
+ * the kernels fetch the scales from `d` (slower, no extra memory).
+ * sub_out: rows*cols/32 fp16 values. */
+int b200moe_q8_prepare(const void* d, int64_t rows, int32_t cols, void* sub_out, void* stream);
 
 /* Packed GGUF blocks -> the planar planes above (types/gguf_interop/layouts.py:
  * 51-60 Q8_0.unpack; :112-153 Q4_K.unpack with _unpack_gguf_i6_scale_mins

@@ -81,6 +81,7 @@ _PROTOS = {
     "b200moe_device_status": (c_int, [_P, POINTER(c_int32)]),
     "b200moe_dequant": (c_int, [_W, c_int, _P, _P]),
     "b200moe_q4k_prepare": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, _P, _P]),
+    "b200moe_q8_prepare": (c_int, [_P, c_int64, c_int32, _P, _P]),
     "b200moe_gguf_unpack_q8_0": (c_int, [_P, c_int64, _P, _P, _P]),
     "b200moe_gguf_unpack_q4_k": (c_int, [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b200moe_router": (c_int, [_P, c_int, c_int32, _L, _P, _P, _P, _P]),

@@ -247,6 +247,11 @@ int b200moe_q4k_prepare(const void* d, const void* dmin, const uint8_t* sh, cons
                             static_cast<cudaStream_t>(stream));
 }
 
+int b200moe_q8_prepare(const void* d, int64_t rows, int32_t cols, void* sub_out, void* stream) {
+  B200_REQUIRE(rows >= 0 && (rows == 0 || (d && sub_out)), "q8_prepare: bad argument");
+  return launch_q8_prepare(d, rows, cols, sub_out, static_cast<cudaStream_t>(stream));
+}
+
 int b200moe_gguf_unpack_q8_0(const uint8_t* raw, int64_t blocks, void* d_out, int8_t* qs_out,
                              void* stream) {
   B200_REQUIRE(blocks >= 0 && (blocks == 0 || (raw && d_out && qs_out)), "gguf_unpack_q8_0: bad argument");

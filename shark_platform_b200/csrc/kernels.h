@@ -22,6 +22,7 @@ int launch_dequant(const b200moe_weight_t* w, int out_dtype, void* out, cudaStre
 int launch_q4k_prepare(const void* d, const void* dmin, const uint8_t* sh, const uint8_t* sl,
                        const uint8_t* mh, const uint8_t* ml, long long blocks, void* sub,
                        cudaStream_t st);
+int launch_q8_prepare(const void* d, long long rows, int cols, void* out, cudaStream_t st);
 int launch_gguf_q8(const uint8_t* raw, long long blocks, void* d, int8_t* qs, cudaStream_t st);
 int launch_gguf_q4k(const uint8_t* raw, long long blocks, void* d, void* dmin, uint8_t* sh,
                     uint8_t* sl, uint8_t* mh, uint8_t* ml, uint8_t* qs, cudaStream_t st);

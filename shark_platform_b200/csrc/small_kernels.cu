@@ -712,6 +712,31 @@ int launch_dequant(const b200moe_weight_t* w, int out_dtype, void* out, cudaStre
   return B200MOE_OK;
 }
 
+// ------------------------------------------------- Q8_0 scale transposition
+// d [rows, K/32] -> [K/256][rows][8]: the eight scales one row needs for a
+// 256-k stage become 16 contiguous bytes and consecutive rows are adjacent, so
+// a stage's scale tile is one contiguous run (one bulk copy instead of one
+// 16-byte TMA request per row).
+__global__ void q8_scales_tile_kernel(const uint4* __restrict__ d, long long rows, int groups,
+                                      uint4* __restrict__ out) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= rows * groups) return;
+  const long long r = i / groups;
+  const int g = static_cast<int>(i % groups);
+  out[static_cast<long long>(g) * rows + r] = d[i];
+}
+
+int launch_q8_prepare(const void* d, long long rows, int cols, void* out, cudaStream_t st) {
+  B200_REQUIRE(cols % 256 == 0, "q8_prepare: cols (%d) must be a multiple of 256", cols);
+  const int groups = cols / 256;
+  const long long n = rows * groups;
+  if (n == 0) return B200MOE_OK;
+  q8_scales_tile_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
+      static_cast<const uint4*>(d), rows, groups, static_cast<uint4*>(out));
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
 // --------------------------------------------------------- Q4_K scale fold
 // One thread per super-block: the eight 6-bit sub-scales / sub-mins
 // (low nibble plane | 2-bit high plane << 4) times d / dmin, each product

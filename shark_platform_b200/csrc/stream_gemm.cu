@@ -39,7 +39,21 @@ struct StreamArgs {
   int out_kperm;        // gate/up only: permute output columns for a Q4_K down matrix
   void* out;
   int32_t* status;
+  // Q8_0 only: scales transposed to [K/256][rows][8] (16 bytes per row and
+  // stage, consecutive rows contiguous); NULL = fetch them as 16-byte TMA rows
+  const uint8_t* st0;
+  const uint8_t* st1;
+  long long total_rows;  // E * N
 };
+
+// Untiled bulk copy global -> shared (both 16-byte aligned, size % 16 == 0).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
 
 template <int LAYOUT, int S>
 struct Cfg {
@@ -96,7 +110,9 @@ template <int LAYOUT, int NMAT, int S>
 __global__ void __launch_bounds__(THREADS, 1)
 stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                    const __grid_constant__ CUtensorMap tm_s0, const __grid_constant__ CUtensorMap tm_s1,
-                   const __grid_constant__ CUtensorMap tm_x, const StreamArgs args) {
+                   const __grid_constant__ CUtensorMap tm_x8, const __grid_constant__ CUtensorMap tm_x16,
+                   const __grid_constant__ CUtensorMap tm_x32, const __grid_constant__ CUtensorMap tm_x64,
+                   const StreamArgs args) {
   using C = Cfg<LAYOUT, S>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -158,13 +174,17 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
         int e, tile, kc, row0, rows;
         decode(item, e, tile, kc, row0, rows);
         const int n0 = tile * (NMAT == 2 ? SET_ROWS : 2 * SET_ROWS);
+        // token boxes no taller than the segment needs (each box row is one TMA request)
+        const CUtensorMap* tx = rows <= 8 ? &tm_x8 : rows <= 16 ? &tm_x16 : rows <= 32 ? &tm_x32 : &tm_x64;
+        const int xrows = rows <= 8 ? 8 : rows <= 16 ? 16 : rows <= 32 ? 32 : 64;
+        const uint32_t tx_bytes = 2 * C::WSET + 2 * C::SSET + 4 * xrows * 128;
         for (int st = 0; st < args.stages_per_item; ++st, ++n) {
           const int slot = n % STAGES;
           const uint32_t phase = (n / STAGES) & 1u;
           if (!mbar_wait(empty_bar(slot), phase ^ 1u, abort_flag, args.status)) { ok = false; break; }
           const uint32_t sb = smem_base + slot * C::STAGE;
           const uint32_t fb = full_bar(slot);
-          mbar_expect_tx(fb, C::STAGE);
+          mbar_expect_tx(fb, tx_bytes);
           const int k0 = (kc * args.stages_per_item + st) * KT;
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
@@ -174,7 +194,14 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
             if constexpr (LAYOUT == B200MOE_LAYOUT_Q8_0) {
               tma_load_2d(sb + r * C::WSET, tw, k0, grow, fb);
               tma_load_2d(sb + r * C::WSET + SET_ROWS * 128, tw, k0 + 128, grow, fb);
-              tma_load_2d(sb + C::OFF_S + r * C::SSET, ts, (k0 / 32) * 2, grow, fb);
+              if (args.st0 != nullptr) {
+                const uint8_t* sp = (NMAT == 2 && r == 1) ? args.st1 : args.st0;
+                bulk_load(sb + C::OFF_S + r * C::SSET,
+                          sp + (static_cast<long long>(k0 / KT) * args.total_rows + grow) * 16,
+                          C::SSET, fb);
+              } else {
+                tma_load_2d(sb + C::OFF_S + r * C::SSET, ts, (k0 / 32) * 2, grow, fb);
+              }
             } else if constexpr (LAYOUT == B200MOE_LAYOUT_Q4_K) {
               tma_load_2d(sb + r * C::WSET, tw, k0 / 2, grow, fb);
               tma_load_2d(sb + C::OFF_S + r * C::SSET, ts, (k0 / 32) * 4, grow, fb);
@@ -186,7 +213,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
           }
 #pragma unroll
           for (int c = 0; c < 4; ++c)
-            tma_load_2d(sb + C::OFF_X + c * C::XBOX, &tm_x, (k0 + 64 * c) * 2, row0, fb);
+            tma_load_2d(sb + C::OFF_X + c * C::XBOX, tx, (k0 + 64 * c) * 2, row0, fb);
         }
       }
       // Do not leave while copies may still land in this CTA's shared memory.
@@ -416,7 +443,8 @@ int launch_t(const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
     B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     configured[dev] = true;
   }
-  kern<<<sm_count(), THREADS, C::SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], a);
+  kern<<<sm_count(), THREADS, C::SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+                                             maps[6], maps[7], a);
   B200_CHECK_CUDA(cudaGetLastError());
   return B200MOE_OK;
 }
@@ -450,6 +478,17 @@ int weight_maps(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts) {
     return rc;
   return make_tmap_2d(ts, w->sub, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, w->cols / 32 * 4,
                       SET_ROWS, 32, false);
+}
+
+// Token-row tensor maps with box heights 8, 16, 32 and 64 (maps[4..7]); heights
+// above the kernel's chunk size 8*S are never selected and alias the largest valid one.
+int token_maps(CUtensorMap* maps, const void* x, int pairs, uint64_t row_bytes, int S) {
+  const int heights[4] = {8, 16, 32, 64};
+  for (int i = 0; i < 4; ++i) {
+    const int hgt = heights[i] <= 8 * S ? heights[i] : 8 * S;
+    if (int rc = make_tmap_2d_sw(&maps[4 + i], x, pairs, row_bytes, hgt, 128, 128)) return rc;
+  }
+  return B200MOE_OK;
 }
 
 int pick_s(int max_segment) {
@@ -501,16 +540,19 @@ int launch_stream_gate_up(const void* xs, const int32_t* seg, int pairs, int max
                gate->rows);
   if (pairs == 0) return B200MOE_OK;
   const int S = pick_s(max_segment);
-  CUtensorMap maps[5];
+  CUtensorMap maps[8];
   if (int rc = weight_maps(gate, &maps[0], &maps[2])) return rc;
   if (int rc = weight_maps(up, &maps[1], &maps[3])) return rc;
-  if (int rc = make_tmap_2d(&maps[4], xs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pairs,
-                            static_cast<uint64_t>(gate->cols) * 2, 8 * S, 128, true))
-    return rc;
+  if (int rc = token_maps(maps, xs, pairs, static_cast<uint64_t>(gate->cols) * 2, S)) return rc;
   StreamArgs a{};
   a.seg = seg; a.E = gate->experts; a.N = gate->rows; a.K = gate->cols;
   a.ntiles = gate->rows / SET_ROWS; a.ksplit = 1; a.stages_per_item = gate->cols / KT;
   a.P = pairs; a.act = act; a.out_kperm = out_kperm; a.out = a_out; a.status = device_status_ptr();
+  if (gate->layout == B200MOE_LAYOUT_Q8_0 && gate->sub != nullptr && up->sub != nullptr) {
+    a.st0 = static_cast<const uint8_t*>(gate->sub);
+    a.st1 = static_cast<const uint8_t*>(up->sub);
+  }
+  a.total_rows = static_cast<long long>(gate->experts) * gate->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
   if (gate->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 2>(S, maps, a, st);
   if (gate->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 2>(S, maps, a, st);
@@ -526,18 +568,19 @@ int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_
                ksplit);
   if (pairs == 0) return B200MOE_OK;
   const int S = pick_s(max_segment);
-  CUtensorMap maps[5];
+  CUtensorMap maps[8];
   if (int rc = weight_maps(down, &maps[0], &maps[2])) return rc;
   maps[1] = maps[0];
   maps[3] = maps[2];
-  if (int rc = make_tmap_2d(&maps[4], a_in, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pairs,
-                            static_cast<uint64_t>(down->cols) * 2, 8 * S, 128, true))
-    return rc;
+  if (int rc = token_maps(maps, a_in, pairs, static_cast<uint64_t>(down->cols) * 2, S)) return rc;
   StreamArgs a{};
   a.seg = seg; a.E = down->experts; a.N = down->rows; a.K = down->cols;
   a.ntiles = down->rows / (2 * SET_ROWS); a.ksplit = ksplit;
   a.stages_per_item = down->cols / KT / ksplit;
   a.P = pairs; a.act = 0; a.out_kperm = 0; a.out = d_out; a.status = device_status_ptr();
+  if (down->layout == B200MOE_LAYOUT_Q8_0 && down->sub != nullptr)
+    a.st0 = a.st1 = static_cast<const uint8_t*>(down->sub);
+  a.total_rows = static_cast<long long>(down->experts) * down->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
   if (down->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 1>(S, maps, a, st);
   if (down->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 1>(S, maps, a, st);

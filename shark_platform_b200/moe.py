@@ -83,7 +83,7 @@ def _unbox(t) -> torch.Tensor:
     raise TypeError(f"expected a tensor, got {type(t).__name__}")
 
 
-def prepare_weight(t: Any) -> PreparedWeight:
+def prepare_weight(t: Any, tile_scales: bool = True) -> PreparedWeight:
     """Turns `ffn_*_exps.weight` (a PlanarQuantizedTensor with a Q8_0 /
     Q4_K planar layout — sharktank's or this package's — or a dense tensor) into
     the descriptor the kernels take.  Q8_0 planes are used in place; Q4_K gets
@@ -112,8 +112,15 @@ def prepare_weight(t: Any) -> PreparedWeight:
             qs = planes["qs"].contiguous().view(torch.int8)
             d = planes["d"].contiguous()
             assert d.dtype == torch.float16 and qs.numel() == e * n * k and d.numel() == e * n * k // 32
-            desc = C.WeightDesc(C.LAYOUT_Q8_0, e, n, k, qs.data_ptr(), d.data_ptr(), None)
-            prep = PreparedWeight(desc, C.LAYOUT_Q8_0, e, n, k, (qs, d))
+            sub = None
+            if k % 256 == 0 and tile_scales:
+                sub = torch.empty_like(d)
+                with torch.cuda.device(qs.device):
+                    C.check(C.lib.b200moe_q8_prepare(_ptr(d), e * n, k, _ptr(sub), _stream()),
+                            "q8_prepare")
+            desc = C.WeightDesc(C.LAYOUT_Q8_0, e, n, k, qs.data_ptr(), d.data_ptr(),
+                                None if sub is None else sub.data_ptr())
+            prep = PreparedWeight(desc, C.LAYOUT_Q8_0, e, n, k, (qs, d) + ((sub,) if sub is not None else ()))
         elif name == "SuperBlockOffsetScaled_4_6_Layout":
             qs = planes["qs"].contiguous().view(torch.uint8)
             assert qs.numel() == e * n * k // 2

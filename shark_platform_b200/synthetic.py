@@ -10,8 +10,7 @@ SuperBlockOffsetScaled_4_6_Layout (types/layouts.py:360-530).
 """
 from __future__ import annotations
 
-import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -171,3 +170,51 @@ def layer_flops(tokens: int, top_k: int, hidden: int, ffn: int) -> int:
     """Expert-GEMM flops of one layer call: three [ffn x hidden] products per
     (token, slot), 2 flops per multiply-add."""
     return tokens * top_k * 3 * 2 * ffn * hidden
+
+
+def case_theta(case: Case, device="cuda"):
+    """The case as a Theta of this package's tensor types on `device`, with the
+    theta keys MoeBlock reads (layers/mixture_of_experts_block.py:31-62)."""
+    from . import types as T
+
+    s = case.spec
+    e, f, d = s.experts, s.ffn, s.hidden
+
+    def weight(planes, shape):
+        if s.kind == DENSE:
+            return T.DefaultPrimitiveTensor(data=planes["w"].to(device))
+        p = {k: v.to(device) for k, v in planes.items()}
+        if s.kind == Q8_0:
+            lay = T.BlockScaledLayout(shape, p["d"], p["qs"])
+        else:
+            lay = T.SuperBlockOffsetScaled_4_6_Layout(shape, **p)
+        return T.PlanarQuantizedTensor(shape=shape, layout=lay)
+
+    tree = {
+        "ffn_gate_inp": {"weight": T.DefaultPrimitiveTensor(data=case.router_w.to(device))},
+        "ffn_norm": {"weight": T.DefaultPrimitiveTensor(data=case.norm_w.to(device))},
+        "ffn_gate_exps": {"weight": weight(case.gate, [e, f, d])},
+        "ffn_up_exps": {"weight": weight(case.up, [e, f, d])},
+        "ffn_down_exps": {"weight": weight(case.down, [e, d, f])},
+    }
+    if case.router_b is not None:
+        tree["ffn_gate_inp"]["bias"] = T.DefaultPrimitiveTensor(data=case.router_b.to(device))
+    if case.out_norm_w is not None:
+        tree["layer_output_norm"] = {"weight": T.DefaultPrimitiveTensor(data=case.out_norm_w.to(device))}
+    return T.Theta(tree)
+
+
+def case_block(case: Case, regime: str = "auto", device="cuda"):
+    """B200MoeBlock for the case (weights uploaded to `device`)."""
+    import torch.nn.functional as F
+
+    from .moe import B200MoeBlock
+
+    s = case.spec
+    act = F.silu if s.activation == "silu" else F.gelu
+    return B200MoeBlock(case_theta(case, device), s.experts, s.top_k, s.eps, act, regime=regime)
+
+
+def case_input(case: Case, device="cuda") -> torch.Tensor:
+    h = case.h.to(device)
+    return h.to(torch.bfloat16) if case.spec.act_dtype == "bf16" else h

@@ -58,45 +58,12 @@ def case_digest(case) -> str:
 
 # ---------------------------------------------------------------- GPU side
 def mirror_theta(case, device="cuda"):
-    """The case as a Theta of this package's mirror types on `device`."""
-    from shark_platform_b200 import types as T
-
-    s = case.spec
-    e, f, d = s.experts, s.ffn, s.hidden
-
-    def weight(planes, shape):
-        if s.kind == syn.DENSE:
-            return T.DefaultPrimitiveTensor(data=planes["w"].to(device))
-        p = {k: v.to(device) for k, v in planes.items()}
-        if s.kind == syn.Q8_0:
-            lay = T.BlockScaledLayout(shape, p["d"], p["qs"])
-        else:
-            lay = T.SuperBlockOffsetScaled_4_6_Layout(shape, **p)
-        return T.PlanarQuantizedTensor(shape=shape, layout=lay)
-
-    tree = {
-        "ffn_gate_inp": {"weight": T.DefaultPrimitiveTensor(data=case.router_w.to(device))},
-        "ffn_norm": {"weight": T.DefaultPrimitiveTensor(data=case.norm_w.to(device))},
-        "ffn_gate_exps": {"weight": weight(case.gate, [e, f, d])},
-        "ffn_up_exps": {"weight": weight(case.up, [e, f, d])},
-        "ffn_down_exps": {"weight": weight(case.down, [e, d, f])},
-    }
-    if case.router_b is not None:
-        tree["ffn_gate_inp"]["bias"] = T.DefaultPrimitiveTensor(data=case.router_b.to(device))
-    if case.out_norm_w is not None:
-        tree["layer_output_norm"] = {"weight": T.DefaultPrimitiveTensor(data=case.out_norm_w.to(device))}
-    return T.Theta(tree)
+    return syn.case_theta(case, device)
 
 
 def b200_block(case, regime="auto", device="cuda"):
-    import torch.nn.functional as F
-    from shark_platform_b200.moe import B200MoeBlock
-
-    s = case.spec
-    act = F.silu if s.activation == "silu" else F.gelu
-    return B200MoeBlock(mirror_theta(case, device), s.experts, s.top_k, s.eps, act, regime=regime)
+    return syn.case_block(case, regime, device)
 
 
 def device_input(case, device="cuda"):
-    h = case.h.to(device)
-    return h.to(torch.bfloat16) if case.spec.act_dtype == "bf16" else h
+    return syn.case_input(case, device)

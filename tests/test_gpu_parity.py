@@ -268,3 +268,28 @@ def test_tensor_and_stream_regimes_agree(M):
     ys = blk.layer.forward(h, regime=M.REGIMES["stream"]).cpu()
     yt = blk.layer.forward(h, regime=M.REGIMES["tensor"]).cpu()
     assert orc.rel_l2(yt - case.h, ys - case.h) < 1e-3
+
+
+def test_stream_kernel_scale_paths_agree(M):
+    """Q8_0 scales fetched as TMA rows from `d` (sub == NULL) and as one bulk copy
+    from the stage-tiled copy give identical results."""
+    from shark_platform_b200 import _cabi as C, types as T
+
+    gen = torch.Generator().manual_seed(31)
+    e, n, k, tokens = 4, 256, 1024, 19
+    planes = syn.q8_0_planes(gen, e, n, k)
+
+    def weight():
+        lay = T.BlockScaledLayout([e, n, k], planes["d"].cuda(), planes["qs"].cuda())
+        return T.PlanarQuantizedTensor(shape=[e, n, k], layout=lay)
+
+    w_tiled = M.prepare_weight(weight(), tile_scales=True)
+    w_rows = M.prepare_weight(weight(), tile_scales=False)
+    assert w_tiled.desc.sub and not w_rows.desc.sub
+    ex = torch.stack([torch.randperm(e, generator=gen)[:2] for _ in range(tokens)])
+    plan = M.route_plan(ex.cuda(), e)
+    xs = (torch.randn(tokens * 2, k, generator=gen)).to(torch.float16).cuda()
+    a = M.grouped_matmul(xs, plan.seg_offsets, w_tiled, tokens, C.REGIME_STREAM)
+    b = M.grouped_matmul(xs, plan.seg_offsets, w_rows, tokens, C.REGIME_STREAM)
+    assert torch.equal(a, b)
+    assert M.device_status() == 0
