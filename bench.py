@@ -250,9 +250,15 @@ def main():
     if world > 1:
         block.backend.profile = False
     soak_steps = 0
-    while ms_total < 500.0 and time.perf_counter() - t_soak < 0.6:
-        y = step()
-        soak_steps += 1
+    if world == 1:
+        while ms_total < 500.0 and time.perf_counter() - t_soak < 0.6:
+            y = step()
+            soak_steps += 1
+    elif ms_total < 500.0:
+        # every rank must run the same number of collective steps
+        soak_steps = max(1, min(2000, int(500.0 / max(ms_step, 1e-3))))
+        for _ in range(soak_steps):
+            y = step()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     if clocks is not None:
