@@ -331,7 +331,7 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
   B200_REQUIRE(pairs == 0 || (a && d_out), "down: NULL buffer");
   const int r = pick_regime(regime, down, max_segment);
   if (r == B200MOE_REGIME_TENSOR)
-    return launch_tc_down(a, seg_offsets, pairs, 128, down, d_out, static_cast<cudaStream_t>(stream));
+    return launch_tc_down(a, seg_offsets, pairs, 192, down, d_out, static_cast<cudaStream_t>(stream));
   return launch_stream_down(a, seg_offsets, pairs, max_segment, down,
                             stream_down_ksplit(down, pairs), d_out,
                             static_cast<cudaStream_t>(stream));

@@ -3,25 +3,33 @@
 //
 // Orientation is "swap-AB" with the A operand in tensor memory: a tile of 128
 // weight rows is M, up to 192 tokens of one expert are N.  Weights never touch
-// shared memory in dequantised form: two warpgroups read the TMA-staged
-// quantised bytes (one thread per weight row), dequantise to fp16 in registers
-// and write the row into tensor memory with tcgen05.st, where it is the A
-// operand of the next MMAs.  The token rows (fp16, K-major, 128-byte swizzle) are
-// the B operand, read from shared memory through a matrix descriptor.  This
-// keeps shared-memory traffic at (quantised bytes + token tile reads), well
-// under the 128 B/clk that an SS-mode MMA with in-smem dequantisation exceeds.
+// shared memory in dequantised form: warps read the TMA-staged quantised bytes
+// (one thread per weight row), dequantise to fp16 in registers and write the
+// row into tensor memory with tcgen05.st, where it is the A operand of the next
+// MMAs.  The token rows (fp16, K-major, 128-byte swizzle) are the B operand, read
+// from shared memory through a matrix descriptor.  Shared memory therefore only
+// carries quantised bytes and token tiles.
 //
 // A CTA holds two row sets per tile, each with its own accumulator:
 // gate rows + up rows of the same 128 columns (SiLU/GELU-gated product in the
 // epilogue), or 256 consecutive rows of the down matrix.
 //
-// Warp roles (576 threads, one CTA per SM, persistent over tiles):
+// Three independent shared-memory rings, because their slots live for very
+// different times:
+//   weights  2 slots x (2 sets x 128 rows x 128 k) int8, 128-byte swizzle;
+//            a slot is free again as soon as the dequant warps have read it
+//   tokens   6 slots x (192 rows x 64 k) fp16; a slot is held until the MMAs
+//            that read it have completed
+//   scales   2 slots x (2 sets x 128 rows x 8) fp16 = 256 k
+//
+// Warp roles (608 threads, one CTA per SM, persistent over tiles):
 //   warps 0-7   group 0: dequantise the even 64-k stages (warps 0-3 set 0,
 //               warps 4-7 set 1; warp w owns TMEM lanes 32(w%4)..+31), epilogue
 //   warps 8-15  group 1: the same for the odd stages, so that one group's
 //               tensor-memory store latency hides behind the other's arithmetic
-//   warp  16    TMA producer (quantised tiles + token tile per stage, scales per 4)
-//   warp  17    TMEM allocation; one lane issues the MMAs and commits
+//   warp  16    TMA producer for weights and scales
+//   warp  17    TMA producer for token tiles
+//   warp  18    TMEM allocation; one lane issues the MMAs and commits
 //
 // Tensor-memory columns (512 allocated): accumulators at 0 and 192 (192 fp32
 // columns each), two A staging slots of 2 x 32 columns at 384..511.
@@ -33,23 +41,30 @@
 namespace b200moe {
 namespace {
 
-constexpr int TC_DQ_WARPS = 16;      // two groups of 8: group g dequantises stages of parity g
-constexpr int TC_THREADS = (TC_DQ_WARPS + 2) * 32;
-constexpr int TC_KT = 64;          // k per stage
-constexpr int TC_ROWS = 128;       // weight rows per set
-constexpr int TC_NTOK = 192;       // token rows of the staged tile / accumulator columns
+constexpr int TC_DQ_WARPS = 16;
+constexpr int TC_WARP_WPROD = TC_DQ_WARPS;
+constexpr int TC_WARP_XPROD = TC_DQ_WARPS + 1;
+constexpr int TC_WARP_MMA = TC_DQ_WARPS + 2;
+constexpr int TC_THREADS = (TC_DQ_WARPS + 3) * 32;
+constexpr int TC_KT = 64;            // k per stage (one token slot, one A slot)
+constexpr int TC_ROWS = 128;         // weight rows per set
+constexpr int TC_NTOK = 192;         // token rows of the staged tile / accumulator columns
 constexpr int TC_MAX_E = 64;
-constexpr int TC_WSET = TC_ROWS * TC_KT;        // quantised bytes per set per stage (Q8_0)
-constexpr int TC_XTILE = TC_NTOK * TC_KT * 2;   // token tile bytes per stage
-constexpr int TC_STAGE = 2 * TC_WSET + TC_XTILE;
-constexpr int TC_STAGES = 5;
-constexpr int TC_SGROUP = 4;                     // stages covered by one scale tile (256 k)
-constexpr int TC_SSLOTS = 3;                     // scale ring depth
-constexpr int TC_SSET = TC_ROWS * 16;            // 8 fp16 scales per row per group
-constexpr int TC_STILE = 2 * TC_SSET;
-constexpr int TC_SMEM = 1024 + TC_STAGES * TC_STAGE + TC_SSLOTS * TC_STILE + 256;
+constexpr int TC_WSLOTS = 2;
+constexpr int TC_WSET = TC_ROWS * 128;          // bytes of one set in a weight slot (128 k)
+constexpr int TC_WSLOT = 2 * TC_WSET;
+constexpr int TC_XSLOTS = 6;
+constexpr int TC_XSLOT = TC_NTOK * TC_KT * 2;
+constexpr int TC_SGROUP = 4;                    // stages covered by one scale tile (256 k)
+constexpr int TC_SSLOTS = 2;
+constexpr int TC_SSET = TC_ROWS * 16;           // 8 fp16 scales per row per group
+constexpr int TC_SSLOT = 2 * TC_SSET;
+constexpr int TC_OFF_X = TC_WSLOTS * TC_WSLOT;
+constexpr int TC_OFF_S = TC_OFF_X + TC_XSLOTS * TC_XSLOT;
+constexpr int TC_OFF_BAR = TC_OFF_S + TC_SSLOTS * TC_SSLOT;
+constexpr int TC_SMEM = 1024 + TC_OFF_BAR + 256;
 constexpr uint32_t TC_COL_ACC0 = 0, TC_COL_ACC1 = 192, TC_COL_A = 384;
-static_assert(TC_STAGE % 1024 == 0, "stage alignment");
+static_assert(TC_WSLOT % 1024 == 0 && TC_XSLOT % 1024 == 0, "slot alignment for the swizzle");
 static_assert(TC_SMEM <= 232448, "shared memory budget");
 
 struct TcArgs {
@@ -61,7 +76,20 @@ struct TcArgs {
   int act;
   void* out;
   int32_t* status;
+  // scales transposed to [K/256][rows][8] (one contiguous run per row tile and
+  // 256-k group) or NULL = fetch them from `d` as 16-byte TMA rows
+  const uint8_t* st0;
+  const uint8_t* st1;
+  long long total_rows;
 };
+
+__device__ __forceinline__ void tc_bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
 
 // ---- tcgen05 wrappers ------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
@@ -145,7 +173,10 @@ template <int NMAT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                const __grid_constant__ CUtensorMap tm_s0, const __grid_constant__ CUtensorMap tm_s1,
-               const __grid_constant__ CUtensorMap tm_x, const TcArgs args) {
+               const __grid_constant__ CUtensorMap tm_x16, const __grid_constant__ CUtensorMap tm_x32,
+               const __grid_constant__ CUtensorMap tm_x64, const __grid_constant__ CUtensorMap tm_x96,
+               const __grid_constant__ CUtensorMap tm_x128, const __grid_constant__ CUtensorMap tm_x192,
+               const TcArgs args) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_seg[TC_MAX_E + 1];
   __shared__ int s_prefix[TC_MAX_E + 1];
@@ -153,34 +184,38 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   __shared__ uint32_t s_tmem;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t scale_base = smem_base + TC_STAGES * TC_STAGE;
-  const uint32_t bar_base = scale_base + TC_SSLOTS * TC_STILE;
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (TC_STAGES + s); };
-  auto a_ready_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + s); };
-  auto a_free_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + 2 + s); };
-  const uint32_t acc_full_bar = bar_base + 8u * (2 * TC_STAGES + 4);
-  const uint32_t acc_empty_bar = bar_base + 8u * (2 * TC_STAGES + 5);
-  auto sfull_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + 6 + s); };
-  auto sempty_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + 6 + TC_SSLOTS + s); };
+  const uint32_t x_base = smem_base + TC_OFF_X;
+  const uint32_t scale_base = smem_base + TC_OFF_S;
+  const uint32_t bar_base = smem_base + TC_OFF_BAR;
+  int nb = 0;
+  auto take = [&](int n) { const uint32_t b = bar_base + 8u * nb; nb += n; return b; };
+  const uint32_t wfull = take(TC_WSLOTS), wempty = take(TC_WSLOTS);
+  const uint32_t xfull = take(TC_XSLOTS), xempty = take(TC_XSLOTS);
+  const uint32_t sfull = take(TC_SSLOTS), sempty = take(TC_SSLOTS);
+  const uint32_t a_ready = take(2), a_free = take(2);
+  const uint32_t acc_full_bar = take(1), acc_empty_bar = take(1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s < TC_STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 8 + 1);
+    for (int s = 0; s < TC_WSLOTS; ++s) {
+      mbar_init(wfull + 8u * s, 1);
+      mbar_init(wempty + 8u * s, TC_DQ_WARPS);
+    }
+    for (int s = 0; s < TC_XSLOTS; ++s) {
+      mbar_init(xfull + 8u * s, 1);
+      mbar_init(xempty + 8u * s, 1);
+    }
+    for (int s = 0; s < TC_SSLOTS; ++s) {
+      mbar_init(sfull + 8u * s, 1);
+      mbar_init(sempty + 8u * s, TC_DQ_WARPS);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(a_ready_bar(s), 256);
-      mbar_init(a_free_bar(s), 1);
+      mbar_init(a_ready + 8u * s, 256);
+      mbar_init(a_free + 8u * s, 1);
     }
     mbar_init(acc_full_bar, 1);
     mbar_init(acc_empty_bar, TC_DQ_WARPS * 32);
-    for (int s = 0; s < TC_SSLOTS; ++s) {
-      mbar_init(sfull_bar(s), 1);
-      mbar_init(sempty_bar(s), TC_DQ_WARPS);
-    }
     fence_mbar_init();
     int run = 0;
     for (int e = 0; e < args.E; ++e) {
@@ -192,7 +227,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     s_seg[args.E] = args.seg[args.E];
     s_prefix[args.E] = run;
   }
-  if (warp == TC_DQ_WARPS + 1) {
+  if (warp == TC_WARP_MMA) {
     tmem_alloc(smem_u32(&s_tmem), 512);
     tmem_relinquish();
   }
@@ -202,7 +237,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   const uint32_t tmem = s_tmem;
   const int total_tiles = s_prefix[args.E];
   volatile int* abort_flag = &s_abort;
-  const int stages_per_tile = args.K / TC_KT;
+  const int stages_per_tile = args.K / TC_KT;  // a multiple of 4
 
   // tile -> (expert, row tile, first token row, token rows, MMA N)
   auto decode = [&](int tile, int& e, int& nt, int& row0, int& rows, int& ncols) {
@@ -220,50 +255,78 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     ncols = (max(rows, 1) + 15) & ~15;
   };
 
-  if (warp == TC_DQ_WARPS) {
-    // ---------------------------------------------------------- TMA producer
+  if (warp == TC_WARP_WPROD) {
+    // ------------------------------------------- TMA producer: weights + scales
+    if (lane == 0) {
+      uint32_t n = 0;  // global stage counter; weight slots advance every 2, scale slots every 4
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int e, nt, row0, rows, ncols;
+        decode(tile, e, nt, row0, rows, ncols);
+        const int grow0 = e * args.N + nt * (NMAT == 2 ? TC_ROWS : 2 * TC_ROWS);
+        const int grow1 = NMAT == 2 ? grow0 : grow0 + TC_ROWS;
+        for (int st = 0; st < stages_per_tile; st += 2, n += 2) {
+          const int k0 = st * TC_KT;
+          if (st % TC_SGROUP == 0) {
+            const uint32_t g = n / TC_SGROUP;
+            const int ss = g % TC_SSLOTS;
+            if (!mbar_wait(sempty + 8u * ss, ((g / TC_SSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+            const uint32_t sdst = scale_base + ss * TC_SSLOT;
+            const uint32_t sb = sfull + 8u * ss;
+            mbar_expect_tx(sb, TC_SSLOT);
+            if (args.st0 != nullptr) {
+              const long long goff = static_cast<long long>(k0 / 256) * args.total_rows;
+              tc_bulk_load(sdst, args.st0 + (goff + grow0) * 16, TC_SSET, sb);
+              tc_bulk_load(sdst + TC_SSET, (NMAT == 2 ? args.st1 : args.st0) + (goff + grow1) * 16, TC_SSET, sb);
+            } else {
+              tma_load_2d(sdst, &tm_s0, (k0 / 32) * 2, grow0, sb);
+              tma_load_2d(sdst + TC_SSET, NMAT == 2 ? &tm_s1 : &tm_s0, (k0 / 32) * 2, grow1, sb);
+            }
+          }
+          const uint32_t wi = n >> 1;
+          const int ws = wi % TC_WSLOTS;
+          if (!mbar_wait(wempty + 8u * ws, ((wi / TC_WSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          const uint32_t wdst = smem_base + ws * TC_WSLOT;
+          const uint32_t wb = wfull + 8u * ws;
+          mbar_expect_tx(wb, TC_WSLOT);
+          tma_load_2d(wdst, &tm_w0, k0, grow0, wb);
+          tma_load_2d(wdst + TC_WSET, NMAT == 2 ? &tm_w1 : &tm_w0, k0, grow1, wb);
+        }
+      }
+      // do not leave while copies may still land in this CTA's shared memory
+      const uint32_t wn = n >> 1;
+      for (uint32_t i = wn > (uint32_t)TC_WSLOTS ? wn - TC_WSLOTS : 0; i < wn; ++i)
+        mbar_wait(wfull + 8u * (i % TC_WSLOTS), (i / TC_WSLOTS) & 1u, abort_flag, args.status);
+      const uint32_t gn = n / TC_SGROUP;
+      for (uint32_t g = gn > (uint32_t)TC_SSLOTS ? gn - TC_SSLOTS : 0; g < gn; ++g)
+        mbar_wait(sfull + 8u * (g % TC_SSLOTS), (g / TC_SSLOTS) & 1u, abort_flag, args.status);
+    }
+  } else if (warp == TC_WARP_XPROD) {
+    // -------------------------------------------------- TMA producer: token tiles
     if (lane == 0) {
       uint32_t n = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int e, nt, row0, rows, ncols;
         decode(tile, e, nt, row0, rows, ncols);
-        const int grow0 = e * args.N + nt * (NMAT == 2 ? TC_ROWS : 2 * TC_ROWS);
+        // the per-SM TMA rate is one 128-byte box row per few clocks, whether or
+        // not the row is used: take the shortest box that covers the tile
+        const CUtensorMap* tx = ncols <= 16 ? &tm_x16 : ncols <= 32 ? &tm_x32 : ncols <= 64 ? &tm_x64
+                              : ncols <= 96 ? &tm_x96 : ncols <= 128 ? &tm_x128 : &tm_x192;
+        const uint32_t xbytes = (ncols <= 16 ? 16 : ncols <= 32 ? 32 : ncols <= 64 ? 64
+                               : ncols <= 96 ? 96 : ncols <= 128 ? 128 : 192) * 128;
         for (int st = 0; st < stages_per_tile; ++st, ++n) {
-          const int slot = n % TC_STAGES;
-          const uint32_t ph = (n / TC_STAGES) & 1u;
-          if (!mbar_wait(empty_bar(slot), ph ^ 1u, abort_flag, args.status)) { ok = false; break; }
-          const uint32_t sb = smem_base + slot * TC_STAGE;
-          const uint32_t fb = full_bar(slot);
-          mbar_expect_tx(fb, TC_STAGE);
-          const int k0 = st * TC_KT;
-          if (st % TC_SGROUP == 0) {
-            // block scales of the next 256 k for both row sets
-            const uint32_t g = n / TC_SGROUP;
-            const int ss = g % TC_SSLOTS;
-            if (!mbar_wait(sempty_bar(ss), ((g / TC_SSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
-            const uint32_t sdst = scale_base + ss * TC_STILE;
-            mbar_expect_tx(sfull_bar(ss), TC_STILE);
-            tma_load_2d(sdst, &tm_s0, (k0 / 32) * 2, grow0, sfull_bar(ss));
-            tma_load_2d(sdst + TC_SSET, NMAT == 2 ? &tm_s1 : &tm_s0, (k0 / 32) * 2,
-                        NMAT == 2 ? grow0 : grow0 + TC_ROWS, sfull_bar(ss));
-          }
-          tma_load_2d(sb, &tm_w0, k0, grow0, fb);
-          tma_load_2d(sb + TC_WSET, NMAT == 2 ? &tm_w1 : &tm_w0, k0,
-                      NMAT == 2 ? grow0 : grow0 + TC_ROWS, fb);
-          tma_load_2d(sb + 2 * TC_WSET, &tm_x, k0 * 2, row0, fb);
+          const int xs = n % TC_XSLOTS;
+          if (!mbar_wait(xempty + 8u * xs, ((n / TC_XSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          const uint32_t xb = xfull + 8u * xs;
+          mbar_expect_tx(xb, xbytes);
+          tma_load_2d(x_base + xs * TC_XSLOT, tx, st * TC_KT * 2, row0, xb);
         }
       }
-      // do not leave while copies may still land in this CTA's shared memory
-      const uint32_t first = n > (uint32_t)TC_STAGES ? n - TC_STAGES : 0;
-      for (uint32_t i = first; i < n; ++i)
-        mbar_wait(full_bar(i % TC_STAGES), (i / TC_STAGES) & 1u, abort_flag, args.status);
-      const uint32_t groups = (n + TC_SGROUP - 1) / TC_SGROUP;
-      const uint32_t gfirst = groups > (uint32_t)TC_SSLOTS ? groups - TC_SSLOTS : 0;
-      for (uint32_t g = gfirst; g < groups; ++g)
-        mbar_wait(sfull_bar(g % TC_SSLOTS), (g / TC_SSLOTS) & 1u, abort_flag, args.status);
+      for (uint32_t i = n > (uint32_t)TC_XSLOTS ? n - TC_XSLOTS : 0; i < n; ++i)
+        mbar_wait(xfull + 8u * (i % TC_XSLOTS), (i / TC_XSLOTS) & 1u, abort_flag, args.status);
     }
-  } else if (warp == TC_DQ_WARPS + 1) {
+  } else if (warp == TC_WARP_MMA) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       uint32_t n = 0, ti = 0;
@@ -275,16 +338,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         if (!mbar_wait(acc_empty_bar, (ti & 1u) ^ 1u, abort_flag, args.status)) break;
         tc_fence_after();
         for (int st = 0; st < stages_per_tile; ++st, ++n) {
-          const int slot = n % TC_STAGES;
+          const int xs = n % TC_XSLOTS;
           const int as = n & 1;
-          if (!mbar_wait(full_bar(slot), (n / TC_STAGES) & 1u, abort_flag, args.status) ||
-              !mbar_wait(a_ready_bar(as), (n >> 1) & 1u, abort_flag, args.status)) {
+          if (!mbar_wait(xfull + 8u * xs, (n / TC_XSLOTS) & 1u, abort_flag, args.status) ||
+              !mbar_wait(a_ready + 8u * as, (n >> 1) & 1u, abort_flag, args.status)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t xaddr = smem_base + slot * TC_STAGE + 2 * TC_WSET;
-          const uint64_t bdesc = smem_desc_sw128(xaddr);
+          const uint64_t bdesc = smem_desc_sw128(x_base + xs * TC_XSLOT);
 #pragma unroll
           for (int j = 0; j < TC_KT / 16; ++j) {
             const uint32_t accum = (st > 0 || j > 0) ? 1u : 0u;
@@ -293,8 +355,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             tc_mma_ts(tmem + TC_COL_ACC0, a0, bd, idesc, accum);
             tc_mma_ts(tmem + TC_COL_ACC1, a0 + 32, bd, idesc, accum);
           }
-          tc_commit(empty_bar(slot));
-          tc_commit(a_free_bar(as));
+          tc_commit(xempty + 8u * xs);
+          tc_commit(a_free + 8u * as);
         }
         if (ok) tc_commit(acc_full_bar);
       }
@@ -306,7 +368,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int wq = warp & 3;                // TMEM lane quarter
     const int row = wq * 32 + lane;         // weight row within the set = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
-    const int sw = (row >> 1) & 3;          // 64-byte swizzle term of this row
+    const int sw = row & 7;                 // 128-byte swizzle term of this row
     uint32_t n = 0, ti = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
@@ -315,23 +377,25 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       for (int sg = 0; sg < stages_per_tile / TC_SGROUP && ok; ++sg) {
         const uint32_t g = n / TC_SGROUP;
         const int ss = g % TC_SSLOTS;
-        if (!mbar_wait(sfull_bar(ss), (g / TC_SSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
+        if (!mbar_wait(sfull + 8u * ss, (g / TC_SSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
         uint32_t scw[4];
-        lds128(scale_base + ss * TC_STILE + set * TC_SSET + row * 16, scw);
+        lds128(scale_base + ss * TC_SSLOT + set * TC_SSET + row * 16, scw);
         __syncwarp();
-        if (lane == 0) mbar_arrive(sempty_bar(ss));
+        if (lane == 0) mbar_arrive(sempty + 8u * ss);
 #pragma unroll
         for (int s4 = 0; s4 < 4; ++s4, ++n) {
           if ((s4 & 1) != grp) continue;
-          const int slot = n % TC_STAGES;
+          // this group's half (64 k = chunks 4*grp .. 4*grp+3) of the weight slot
+          const uint32_t wi = n >> 1;
+          const int ws = wi % TC_WSLOTS;
           const int as = n & 1;
-          if (!mbar_wait(full_bar(slot), (n / TC_STAGES) & 1u, abort_flag, args.status)) { ok = false; break; }
-          const uint32_t wrow = smem_base + slot * TC_STAGE + set * TC_WSET + row * 64;
+          if (!mbar_wait(wfull + 8u * ws, (wi / TC_WSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
+          const uint32_t wrow = smem_base + ws * TC_WSLOT + set * TC_WSET + row * 128;
           uint32_t q[4][4];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) lds128(wrow + ((c ^ sw) << 4), q[c]);
+          for (int c = 0; c < 4; ++c) lds128(wrow + (((4 * grp + c) ^ sw) << 4), q[c]);
           __syncwarp();
-          if (lane == 0) mbar_arrive(empty_bar(slot));
+          if (lane == 0) mbar_arrive(wempty + 8u * ws);
           uint32_t v[32];
           const __half2 s_lo = u32_as_h2(__byte_perm(scw[s4], scw[s4], 0x1010));
           const __half2 s_hi = u32_as_h2(__byte_perm(scw[s4], scw[s4], 0x3232));
@@ -340,12 +404,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 4; ++j)
               dequant_q8x4(q[c][j], c < 2 ? s_lo : s_hi, v[c * 8 + 2 * j], v[c * 8 + 2 * j + 1]);
-          if (!mbar_wait(a_free_bar(as), ((n >> 1) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          if (!mbar_wait(a_free + 8u * as, ((n >> 1) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
           tc_fence_after();
           tmem_st32(tmem + lane_addr + TC_COL_A + as * 64 + set * 32, v);
           tmem_wait_st();
           tc_fence_before();
-          mbar_arrive(a_ready_bar(as));
+          mbar_arrive(a_ready + 8u * as);
         }
       }
       if (!ok) break;
@@ -383,7 +447,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   // ---- teardown: everyone is done with tensor memory before it is freed
   tc_fence_before();
   __syncthreads();
-  if (warp == TC_DQ_WARPS + 1) {
+  if (warp == TC_WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -399,8 +463,17 @@ int tc_launch(const CUtensorMap* maps, const TcArgs& a, cudaStream_t st) {
     B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
     configured[dev] = true;
   }
-  kern<<<sm_count(), TC_THREADS, TC_SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], a);
+  kern<<<sm_count(), TC_THREADS, TC_SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+                                                maps[6], maps[7], maps[8], maps[9], a);
   B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+// Token-tile tensor maps with box heights 16, 32, 64, 96, 128 and 192 (maps[4..9]).
+int tc_token_maps(CUtensorMap* maps, const void* x, int pairs, uint64_t row_bytes) {
+  const int heights[6] = {16, 32, 64, 96, 128, 192};
+  for (int i = 0; i < 6; ++i)
+    if (int rc = make_tmap_2d_sw(&maps[4 + i], x, pairs, row_bytes, heights[i], 128, 128)) return rc;
   return B200MOE_OK;
 }
 
@@ -417,10 +490,10 @@ int tc_check(const b200moe_weight_t* w, const char* name) {
 }
 
 int tc_weight_map(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts) {
-  // 64-byte wide boxes of int8 with the 64-byte swizzle: 128 rows x 64 k;
+  // 128-byte wide boxes of int8 with the 128-byte swizzle: 128 rows x 128 k;
   // scale boxes of 8 fp16 (256 k) x 128 rows, unswizzled
   const uint64_t rows = static_cast<uint64_t>(w->experts) * w->rows;
-  if (int rc = make_tmap_2d_sw(tw, w->qs, rows, w->cols, TC_ROWS, 64, 64)) return rc;
+  if (int rc = make_tmap_2d_sw(tw, w->qs, rows, w->cols, TC_ROWS, 128, 128)) return rc;
   return make_tmap_2d_sw(ts, w->d, rows, static_cast<uint64_t>(w->cols) / 32 * 2, TC_ROWS, 16, 0);
 }
 
@@ -439,15 +512,19 @@ int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_til
                "tensor kernel: gate and up shapes differ");
   B200_REQUIRE(gate->rows % TC_ROWS == 0, "tensor kernel: ffn (%d) must be a multiple of 128", gate->rows);
   if (pairs == 0) return B200MOE_OK;
-  CUtensorMap maps[5];
+  CUtensorMap maps[10];
   if (int rc = tc_weight_map(gate, &maps[0], &maps[2])) return rc;
   if (int rc = tc_weight_map(up, &maps[1], &maps[3])) return rc;
-  if (int rc = make_tmap_2d_sw(&maps[4], xs, pairs, static_cast<uint64_t>(gate->cols) * 2, TC_NTOK, 128, 128))
-    return rc;
+  if (int rc = tc_token_maps(maps, xs, pairs, static_cast<uint64_t>(gate->cols) * 2)) return rc;
   TcArgs a{};
   a.seg = seg; a.E = gate->experts; a.N = gate->rows; a.K = gate->cols;
   a.ntiles = gate->rows / TC_ROWS; a.tok_tile = tok_tile; a.P = pairs; a.act = act;
   a.out = a_out; a.status = device_status_ptr();
+  if (gate->sub != nullptr && up->sub != nullptr) {
+    a.st0 = static_cast<const uint8_t*>(gate->sub);
+    a.st1 = static_cast<const uint8_t*>(up->sub);
+  }
+  a.total_rows = static_cast<long long>(gate->experts) * gate->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
   return tc_launch<2>(maps, a, st);
 }
@@ -458,16 +535,17 @@ int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile
   B200_REQUIRE(down->rows % (2 * TC_ROWS) == 0, "tensor kernel: hidden (%d) must be a multiple of 256",
                down->rows);
   if (pairs == 0) return B200MOE_OK;
-  CUtensorMap maps[5];
+  CUtensorMap maps[10];
   if (int rc = tc_weight_map(down, &maps[0], &maps[2])) return rc;
   maps[1] = maps[0];
   maps[3] = maps[2];
-  if (int rc = make_tmap_2d_sw(&maps[4], a_in, pairs, static_cast<uint64_t>(down->cols) * 2, TC_NTOK, 128, 128))
-    return rc;
+  if (int rc = tc_token_maps(maps, a_in, pairs, static_cast<uint64_t>(down->cols) * 2)) return rc;
   TcArgs a{};
   a.seg = seg; a.E = down->experts; a.N = down->rows; a.K = down->cols;
   a.ntiles = down->rows / (2 * TC_ROWS); a.tok_tile = tok_tile; a.P = pairs; a.act = 0;
   a.out = d_out; a.status = device_status_ptr();
+  if (down->sub != nullptr) a.st0 = a.st1 = static_cast<const uint8_t*>(down->sub);
+  a.total_rows = static_cast<long long>(down->experts) * down->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
   return tc_launch<1>(maps, a, st);
 }
