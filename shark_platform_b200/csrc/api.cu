@@ -296,7 +296,8 @@ int b200moe_permute_rows(const void* xn, const int32_t* perm, const int32_t* seg
 int b200moe_kperm(int layout, int regime, int32_t max_segment) {
   (void)regime;
   (void)max_segment;
-  // Q4_K runs in the streaming kernel only, which wants interleaved columns.
+  // both Q4_K kernels pull nibble pairs (q_i, q_i+4) out of a word and want
+  // the matching column interleave
   return layout == B200MOE_LAYOUT_Q4_K ? 1 : 0;
 }
 
@@ -310,8 +311,7 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
                "gate_up: unknown activation %d", activation);
   const int r = pick_regime(regime, gate, max_segment);
   if (r == B200MOE_REGIME_TENSOR) {
-    B200_REQUIRE(!out_kperm, "gate_up: the tensor regime writes natural column order");
-    return launch_tc_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, a_out,
+    return launch_tc_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, out_kperm, a_out,
                              static_cast<cudaStream_t>(stream));
   }
   return launch_stream_gate_up(xs, seg_offsets, pairs, max_segment, gate, up, activation,

@@ -169,6 +169,26 @@ __device__ __forceinline__ void dequant_q8x4(uint32_t w, __half2 scale, uint32_t
   hi = h2_as_u32(__hmul2(h, scale));
 }
 
+// Eight 4-bit quants of one 32-bit word (k order: nibble i of byte b is
+// element 2b+i) -> fp16(fp16(ds*q) - dm) as four half2 whose element pairs are
+// (q0,q4) (q1,q5) (q2,q6) (q3,q7): the pair order the activation rows are
+// pre-permuted to.  0x6400|q is 1024+q exactly, so one subtraction gives q.
+__device__ __forceinline__ void dequant_q4x8(uint32_t w, __half2 ds, __half2 dm,
+                                             uint32_t (&out)[4]) {
+  const __half2 k1024 = u32_as_h2(0x64006400u);
+  const uint32_t w1 = w >> 8;
+  uint32_t e[4];
+  e[0] = (w & 0x000f000fu) | 0x64006400u;          // (q0, q4)
+  e[1] = ((w >> 4) & 0x000f000fu) | 0x64006400u;   // (q1, q5)
+  e[2] = (w1 & 0x000f000fu) | 0x64006400u;         // (q2, q6)
+  e[3] = ((w1 >> 4) & 0x000f000fu) | 0x64006400u;  // (q3, q7)
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 q = __hsub2(u32_as_h2(e[i]), k1024);
+    out[i] = h2_as_u32(__hsub2_rn(__hmul2_rn(ds, q), dm));  // _rn: no fma contraction
+  }
+}
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float gelu_erf_f(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));

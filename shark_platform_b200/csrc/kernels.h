@@ -39,7 +39,7 @@ int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_
 bool tc_supported(const b200moe_weight_t* w);
 int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_tile,
                       const b200moe_weight_t* gate, const b200moe_weight_t* up, int act,
-                      void* a_out, cudaStream_t st);
+                      int out_kperm, void* a_out, cudaStream_t st);
 int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile,
                    const b200moe_weight_t* down, float* d_out, cudaStream_t st);
 

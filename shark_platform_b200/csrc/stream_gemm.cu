@@ -86,26 +86,6 @@ __device__ __forceinline__ __half2 bcast_half(uint32_t v, int sel) {
   return u32_as_h2(__byte_perm(v, v, sel ? 0x3232 : 0x1010));
 }
 
-// Eight 4-bit quants of one 32-bit word (k order: nibble i of byte b is
-// element 2b+i) -> fp16(fp16(ds*q) - dm) as four half2 whose element pairs are
-// (q0,q4) (q1,q5) (q2,q6) (q3,q7): the pair order the activation rows are
-// pre-permuted to.  0x6400|q is 1024+q exactly, so one subtraction gives q.
-__device__ __forceinline__ void dequant_q4x8(uint32_t w, __half2 ds, __half2 dm,
-                                             uint32_t (&out)[4]) {
-  const __half2 k1024 = u32_as_h2(0x64006400u);
-  const uint32_t w1 = w >> 8;
-  uint32_t e[4];
-  e[0] = (w & 0x000f000fu) | 0x64006400u;          // (q0, q4)
-  e[1] = ((w >> 4) & 0x000f000fu) | 0x64006400u;   // (q1, q5)
-  e[2] = (w1 & 0x000f000fu) | 0x64006400u;         // (q2, q6)
-  e[3] = ((w1 >> 4) & 0x000f000fu) | 0x64006400u;  // (q3, q7)
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __half2 q = __hsub2(u32_as_h2(e[i]), k1024);
-    out[i] = h2_as_u32(__hsub2_rn(__hmul2_rn(ds, q), dm));  // _rn: no fma contraction
-  }
-}
-
 template <int LAYOUT, int NMAT, int S>
 __global__ void __launch_bounds__(THREADS, 1)
 stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,

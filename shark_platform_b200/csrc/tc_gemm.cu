@@ -57,7 +57,7 @@ constexpr int TC_XSLOTS = 6;
 constexpr int TC_XSLOT = TC_NTOK * TC_KT * 2;
 constexpr int TC_SGROUP = 4;                    // stages covered by one scale tile (256 k)
 constexpr int TC_SSLOTS = 2;
-constexpr int TC_SSET = TC_ROWS * 16;           // 8 fp16 scales per row per group
+constexpr int TC_SSET = TC_ROWS * 32;           // per row and group: 8 fp16 scales (Q8_0, 16 B used) or 8 half2 scale/min pairs (Q4_K)
 constexpr int TC_SSLOT = 2 * TC_SSET;
 constexpr int TC_OFF_X = TC_WSLOTS * TC_WSLOT;
 constexpr int TC_OFF_S = TC_OFF_X + TC_XSLOTS * TC_XSLOT;
@@ -74,6 +74,7 @@ struct TcArgs {
   int tok_tile;    // upper bound on tokens per tile (multiple of 16, <= 192)
   int P;
   int act;
+  int out_kperm;   // gate/up only: interleave output columns for a Q4_K down matrix
   void* out;
   int32_t* status;
   // scales transposed to [K/256][rows][8] (one contiguous run per row tile and
@@ -169,7 +170,7 @@ __device__ __forceinline__ uint32_t make_idesc(int m, int n) {
   return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-template <int NMAT>
+template <int LAYOUT, int NMAT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                const __grid_constant__ CUtensorMap tm_s0, const __grid_constant__ CUtensorMap tm_s1,
@@ -238,6 +239,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   const int total_tiles = s_prefix[args.E];
   volatile int* abort_flag = &s_abort;
   const int stages_per_tile = args.K / TC_KT;  // a multiple of 4
+  constexpr bool Q4 = LAYOUT == B200MOE_LAYOUT_Q4_K;
+  constexpr uint32_t WSET_BYTES = Q4 ? TC_ROWS * 64 : TC_ROWS * 128;  // one set, 128 k
+  constexpr uint32_t SSET_BYTES = Q4 ? TC_ROWS * 32 : TC_ROWS * 16;   // one set, 256 k
 
   // tile -> (expert, row tile, first token row, token rows, MMA N)
   auto decode = [&](int tile, int& e, int& nt, int& row0, int& rows, int& ncols) {
@@ -273,11 +277,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             if (!mbar_wait(sempty + 8u * ss, ((g / TC_SSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
             const uint32_t sdst = scale_base + ss * TC_SSLOT;
             const uint32_t sb = sfull + 8u * ss;
-            mbar_expect_tx(sb, TC_SSLOT);
-            if (args.st0 != nullptr) {
+            mbar_expect_tx(sb, 2 * SSET_BYTES);
+            if constexpr (Q4) {
+              tma_load_2d(sdst, &tm_s0, (k0 / 32) * 4, grow0, sb);
+              tma_load_2d(sdst + TC_SSET, NMAT == 2 ? &tm_s1 : &tm_s0, (k0 / 32) * 4, grow1, sb);
+            } else if (args.st0 != nullptr) {
               const long long goff = static_cast<long long>(k0 / 256) * args.total_rows;
-              tc_bulk_load(sdst, args.st0 + (goff + grow0) * 16, TC_SSET, sb);
-              tc_bulk_load(sdst + TC_SSET, (NMAT == 2 ? args.st1 : args.st0) + (goff + grow1) * 16, TC_SSET, sb);
+              tc_bulk_load(sdst, args.st0 + (goff + grow0) * 16, SSET_BYTES, sb);
+              tc_bulk_load(sdst + TC_SSET, (NMAT == 2 ? args.st1 : args.st0) + (goff + grow1) * 16, SSET_BYTES, sb);
             } else {
               tma_load_2d(sdst, &tm_s0, (k0 / 32) * 2, grow0, sb);
               tma_load_2d(sdst + TC_SSET, NMAT == 2 ? &tm_s1 : &tm_s0, (k0 / 32) * 2, grow1, sb);
@@ -288,9 +295,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           if (!mbar_wait(wempty + 8u * ws, ((wi / TC_WSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
           const uint32_t wdst = smem_base + ws * TC_WSLOT;
           const uint32_t wb = wfull + 8u * ws;
-          mbar_expect_tx(wb, TC_WSLOT);
-          tma_load_2d(wdst, &tm_w0, k0, grow0, wb);
-          tma_load_2d(wdst + TC_WSET, NMAT == 2 ? &tm_w1 : &tm_w0, k0, grow1, wb);
+          mbar_expect_tx(wb, 2 * WSET_BYTES);
+          tma_load_2d(wdst, &tm_w0, Q4 ? k0 / 2 : k0, grow0, wb);
+          tma_load_2d(wdst + TC_WSET, NMAT == 2 ? &tm_w1 : &tm_w0, Q4 ? k0 / 2 : k0, grow1, wb);
         }
       }
       // do not leave while copies may still land in this CTA's shared memory
@@ -378,32 +385,58 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         const uint32_t g = n / TC_SGROUP;
         const int ss = g % TC_SSLOTS;
         if (!mbar_wait(sfull + 8u * ss, (g / TC_SSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
-        uint32_t scw[4];
-        lds128(scale_base + ss * TC_SSLOT + set * TC_SSET + row * 16, scw);
+        // Q8_0: 8 fp16 block scales of the 256-k group; Q4_K: 8 (scale, min) half2 pairs
+        uint32_t scw[8];
+        if constexpr (Q4) {
+          lds128(scale_base + ss * TC_SSLOT + set * TC_SSET + row * 32, *reinterpret_cast<uint32_t(*)[4]>(&scw[0]));
+          lds128(scale_base + ss * TC_SSLOT + set * TC_SSET + row * 32 + 16, *reinterpret_cast<uint32_t(*)[4]>(&scw[4]));
+        } else {
+          lds128(scale_base + ss * TC_SSLOT + set * TC_SSET + row * 16, *reinterpret_cast<uint32_t(*)[4]>(&scw[0]));
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(sempty + 8u * ss);
 #pragma unroll
         for (int s4 = 0; s4 < 4; ++s4, ++n) {
           if ((s4 & 1) != grp) continue;
-          // this group's half (64 k = chunks 4*grp .. 4*grp+3) of the weight slot
+          // this group's half (64 k) of the weight slot
           const uint32_t wi = n >> 1;
           const int ws = wi % TC_WSLOTS;
           const int as = n & 1;
           if (!mbar_wait(wfull + 8u * ws, (wi / TC_WSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
-          const uint32_t wrow = smem_base + ws * TC_WSLOT + set * TC_WSET + row * 128;
-          uint32_t q[4][4];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) lds128(wrow + (((4 * grp + c) ^ sw) << 4), q[c]);
-          __syncwarp();
-          if (lane == 0) mbar_arrive(wempty + 8u * ws);
           uint32_t v[32];
-          const __half2 s_lo = u32_as_h2(__byte_perm(scw[s4], scw[s4], 0x1010));
-          const __half2 s_hi = u32_as_h2(__byte_perm(scw[s4], scw[s4], 0x3232));
+          if constexpr (Q4) {
+            // 64-byte rows (128 k of nibbles), 64-byte swizzle; this stage = chunks 2*grp, 2*grp+1
+            const uint32_t wrow = smem_base + ws * TC_WSLOT + set * TC_WSET + row * 64;
+            const int sw64 = (row >> 1) & 3;
+            uint32_t q[2][4];
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c) lds128(wrow + (((2 * grp + c) ^ sw64) << 4), q[c]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(wempty + 8u * ws);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              dequant_q8x4(q[c][j], c < 2 ? s_lo : s_hi, v[c * 8 + 2 * j], v[c * 8 + 2 * j + 1]);
+            for (int c = 0; c < 2; ++c) {
+              const uint32_t sm = scw[2 * s4 + c];  // sub-block (32 k) scale / min
+              const __half2 ds = u32_as_h2(__byte_perm(sm, sm, 0x1010));
+              const __half2 dm = u32_as_h2(__byte_perm(sm, sm, 0x3232));
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                dequant_q4x8(q[c][j], ds, dm, *reinterpret_cast<uint32_t(*)[4]>(&v[c * 16 + j * 4]));
+            }
+          } else {
+            const uint32_t wrow = smem_base + ws * TC_WSLOT + set * TC_WSET + row * 128;
+            uint32_t q[4][4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) lds128(wrow + (((4 * grp + c) ^ sw) << 4), q[c]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(wempty + 8u * ws);
+            const __half2 s_lo = u32_as_h2(__byte_perm(scw[s4], scw[s4], 0x1010));
+            const __half2 s_hi = u32_as_h2(__byte_perm(scw[s4], scw[s4], 0x3232));
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                dequant_q8x4(q[c][j], c < 2 ? s_lo : s_hi, v[c * 8 + 2 * j], v[c * 8 + 2 * j + 1]);
+          }
           if (!mbar_wait(a_free + 8u * as, ((n >> 1) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
           tc_fence_after();
           tmem_st32(tmem + lane_addr + TC_COL_A + as * 64 + set * 32, v);
@@ -429,8 +462,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           if constexpr (NMAT == 2) {
             const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
             const float a = args.act == B200MOE_ACT_SILU ? silu_f(gv) : gelu_erf_f(gv);
-            static_cast<__half*>(args.out)[static_cast<size_t>(tok) * args.N + nt * TC_ROWS + row] =
-                to_half_sat(a * uv);
+            int col = nt * TC_ROWS + row;
+            if (args.out_kperm) col = (col & ~7) | ((col & 3) << 1) | ((col >> 2) & 1);
+            static_cast<__half*>(args.out)[static_cast<size_t>(tok) * args.N + col] = to_half_sat(a * uv);
           } else {
             float* o = static_cast<float*>(args.out) + static_cast<size_t>(tok) * args.N +
                        nt * (2 * TC_ROWS) + row;
@@ -453,9 +487,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   }
 }
 
-template <int NMAT>
+template <int LAYOUT, int NMAT>
 int tc_launch(const CUtensorMap* maps, const TcArgs& a, cudaStream_t st) {
-  auto kern = tc_gemm_kernel<NMAT>;
+  auto kern = tc_gemm_kernel<LAYOUT, NMAT>;
   static bool configured[16] = {};
   int dev = 0;
   B200_CHECK_CUDA(cudaGetDevice(&dev));
@@ -478,13 +512,14 @@ int tc_token_maps(CUtensorMap* maps, const void* x, int pairs, uint64_t row_byte
 }
 
 int tc_check(const b200moe_weight_t* w, const char* name) {
-  B200_REQUIRE(w->layout == B200MOE_LAYOUT_Q8_0, "tensor kernel: %s must be Q8_0 (layout %d)", name,
-               w->layout);
+  B200_REQUIRE(w->layout == B200MOE_LAYOUT_Q8_0 || w->layout == B200MOE_LAYOUT_Q4_K,
+               "tensor kernel: %s must be Q8_0 or Q4_K (layout %d)", name, w->layout);
   B200_REQUIRE(w->cols % 256 == 0, "tensor kernel: %s cols (%d) must be a multiple of 256", name,
                w->cols);
   B200_REQUIRE(w->experts >= 1 && w->experts <= TC_MAX_E, "tensor kernel: %s experts out of range", name);
-  B200_REQUIRE(w->qs && w->d && (reinterpret_cast<uintptr_t>(w->qs) & 15) == 0 &&
-                   (reinterpret_cast<uintptr_t>(w->d) & 15) == 0,
+  const void* sc = w->layout == B200MOE_LAYOUT_Q8_0 ? w->d : w->sub;
+  B200_REQUIRE(w->qs && sc && (reinterpret_cast<uintptr_t>(w->qs) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(sc) & 15) == 0,
                "tensor kernel: %s planes missing or misaligned", name);
   return B200MOE_OK;
 }
@@ -493,6 +528,11 @@ int tc_weight_map(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts) {
   // 128-byte wide boxes of int8 with the 128-byte swizzle: 128 rows x 128 k;
   // scale boxes of 8 fp16 (256 k) x 128 rows, unswizzled
   const uint64_t rows = static_cast<uint64_t>(w->experts) * w->rows;
+  if (w->layout == B200MOE_LAYOUT_Q4_K) {
+    // nibbles: 64-byte wide boxes (128 k), 64-byte swizzle; (scale, min) pairs: 32 bytes per row
+    if (int rc = make_tmap_2d_sw(tw, w->qs, rows, w->cols / 2, TC_ROWS, 64, 64)) return rc;
+    return make_tmap_2d_sw(ts, w->sub, rows, static_cast<uint64_t>(w->cols) / 32 * 4, TC_ROWS, 32, 0);
+  }
   if (int rc = make_tmap_2d_sw(tw, w->qs, rows, w->cols, TC_ROWS, 128, 128)) return rc;
   return make_tmap_2d_sw(ts, w->d, rows, static_cast<uint64_t>(w->cols) / 32 * 2, TC_ROWS, 16, 0);
 }
@@ -500,16 +540,17 @@ int tc_weight_map(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts) {
 }  // namespace
 
 bool tc_supported(const b200moe_weight_t* w) {
-  return w->layout == B200MOE_LAYOUT_Q8_0 && w->cols % 256 == 0;
+  return (w->layout == B200MOE_LAYOUT_Q8_0 || w->layout == B200MOE_LAYOUT_Q4_K) && w->cols % 256 == 0;
 }
 
 int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_tile,
                       const b200moe_weight_t* gate, const b200moe_weight_t* up, int act,
-                      void* a_out, cudaStream_t st) {
+                      int out_kperm, void* a_out, cudaStream_t st) {
   if (int rc = tc_check(gate, "gate")) return rc;
   if (int rc = tc_check(up, "up")) return rc;
-  B200_REQUIRE(gate->rows == up->rows && gate->cols == up->cols && gate->experts == up->experts,
-               "tensor kernel: gate and up shapes differ");
+  B200_REQUIRE(gate->rows == up->rows && gate->cols == up->cols && gate->experts == up->experts &&
+                   gate->layout == up->layout,
+               "tensor kernel: gate and up shapes or layouts differ");
   B200_REQUIRE(gate->rows % TC_ROWS == 0, "tensor kernel: ffn (%d) must be a multiple of 128", gate->rows);
   if (pairs == 0) return B200MOE_OK;
   CUtensorMap maps[10];
@@ -519,14 +560,16 @@ int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_til
   TcArgs a{};
   a.seg = seg; a.E = gate->experts; a.N = gate->rows; a.K = gate->cols;
   a.ntiles = gate->rows / TC_ROWS; a.tok_tile = tok_tile; a.P = pairs; a.act = act;
+  a.out_kperm = out_kperm;
   a.out = a_out; a.status = device_status_ptr();
+  a.total_rows = static_cast<long long>(gate->experts) * gate->rows;
+  if (a.status == nullptr) return B200MOE_ERR_CUDA;
+  if (gate->layout == B200MOE_LAYOUT_Q4_K) return tc_launch<B200MOE_LAYOUT_Q4_K, 2>(maps, a, st);
   if (gate->sub != nullptr && up->sub != nullptr) {
     a.st0 = static_cast<const uint8_t*>(gate->sub);
     a.st1 = static_cast<const uint8_t*>(up->sub);
   }
-  a.total_rows = static_cast<long long>(gate->experts) * gate->rows;
-  if (a.status == nullptr) return B200MOE_ERR_CUDA;
-  return tc_launch<2>(maps, a, st);
+  return tc_launch<B200MOE_LAYOUT_Q8_0, 2>(maps, a, st);
 }
 
 int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile,
@@ -544,10 +587,11 @@ int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile
   a.seg = seg; a.E = down->experts; a.N = down->rows; a.K = down->cols;
   a.ntiles = down->rows / (2 * TC_ROWS); a.tok_tile = tok_tile; a.P = pairs; a.act = 0;
   a.out = d_out; a.status = device_status_ptr();
-  if (down->sub != nullptr) a.st0 = a.st1 = static_cast<const uint8_t*>(down->sub);
   a.total_rows = static_cast<long long>(down->experts) * down->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
-  return tc_launch<1>(maps, a, st);
+  if (down->layout == B200MOE_LAYOUT_Q4_K) return tc_launch<B200MOE_LAYOUT_Q4_K, 1>(maps, a, st);
+  if (down->sub != nullptr) a.st0 = a.st1 = static_cast<const uint8_t*>(down->sub);
+  return tc_launch<B200MOE_LAYOUT_Q8_0, 1>(maps, a, st);
 }
 
 }  // namespace b200moe

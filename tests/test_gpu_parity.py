@@ -235,7 +235,7 @@ def test_ops_decline_unsupported():
 
 
 # ------------------------------------------------ tensor-memory (tcgen05) regime
-@pytest.mark.parametrize("name", ["small_q8", "small_grok", "small_top4"])
+@pytest.mark.parametrize("name", ["small_q8", "small_grok", "small_top4", "small_q4k"])
 def test_tensor_regime_matches_reference_fixture(M, name):
     g = load_golden(f"moe_{name}.npz")
     case = syn.make_case(syn.CASES[name])
@@ -248,8 +248,9 @@ def test_tensor_regime_matches_reference_fixture(M, name):
 
 
 @pytest.mark.parametrize("tokens", [1, 15, 16, 17, 100, 193, 400, 777])
-def test_tensor_regime_ragged_token_counts(M, tokens):
-    spec = syn.CaseSpec("ragged_tc", tokens, 512, 1024, kind=syn.Q8_0, norm_weight="perturbed",
+@pytest.mark.parametrize("kind", [syn.Q8_0, syn.Q4_K])
+def test_tensor_regime_ragged_token_counts(M, tokens, kind):
+    spec = syn.CaseSpec("ragged_tc", tokens, 512, 1024, kind=kind, norm_weight="perturbed",
                         seed=300 + tokens, act_dtype="f32")
     case = syn.make_case(spec)
     want, mid = orc.moe_block(case.h, oracle_params(case), form="per_expert")
