@@ -8,6 +8,10 @@ top-2, SiLU, Q8_0 weights, bf16 activations, seeded synthetic values):
   prefill4096  4096 tokens (default; tensor-core bound)
   decode32     32 tokens   (HBM bound: the weights are streamed once per call)
   decode1 / decode128
+  q4k_decode32 / q4k_prefill2048   the same layer with Q4_K expert weights
+  grok_prefill8192                 Grok-1 shape (hidden 6144, ffn 32768, GELU, output norm)
+  stack32_decode64                 32 Mixtral layers back to back, 64 tokens, Zipf(1.2)
+                                   router bias per layer (weights drawn on the device)
 
 With N > 1 (torchrun, one process per GPU) the experts are partitioned over the
 ranks, each rank routes tokens/N tokens and the token rows move by NCCL
@@ -38,6 +42,10 @@ WORKLOADS = {
     "decode32": ("mixtral_q8", 32),
     "decode1": ("mixtral_q8", 1),
     "decode128": ("mixtral_q8", 128),
+    "q4k_decode32": ("mixtral_q4k", 32),
+    "q4k_prefill2048": ("mixtral_q4k", 2048),
+    "grok_prefill8192": ("grok_q8", 8192),
+    "stack32_decode64": ("mixtral_q8", 64),
 }
 STAGES = ["router", "route_plan", "permute", "gate_up", "down", "combine"]
 
@@ -133,7 +141,8 @@ def run_reference(args, spec_name, tokens):
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     sample = min(tokens, 8)
-    case = syn.make_case(syn.CASES[spec_name], tokens=sample)
+    spec = syn.CASES[spec_name]
+    case = syn.make_case(spec, tokens=sample)
     params, h, _ = cpu_reference_setup(case, sample)
     steps, warmup = min(args.steps, 8), min(args.warmup, 1)
     tps, per_step = time_cpu(params, h, steps, warmup)
@@ -144,8 +153,10 @@ def run_reference(args, spec_name, tokens):
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": per_step * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": args.workload, "layer": "mixtral-8x7b MoE FFN, Q8_0 experts",
-                   "tokens": tokens, "hidden": 4096, "ffn": 14336, "experts": 8, "top_k": 2},
+        "config": {"workload": args.workload,
+                   "layer": f"{spec_name} MoE FFN ({spec.kind} experts, {spec.activation})",
+                   "tokens": tokens, "hidden": spec.hidden, "ffn": spec.ffn,
+                   "experts": spec.experts, "top_k": spec.top_k},
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": sample_txt},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -188,7 +199,23 @@ def main():
     flops = syn.layer_flops(tokens, spec.top_k, spec.hidden, spec.ffn)
     w_bytes_expert = 3 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
 
-    if world == 1:
+    layers = 1
+    if args.workload == "stack32_decode64":
+        assert world == 1, "the layer stack runs on one GPU in this build"
+        from shark_platform_b200.moe import B200MoeStack
+        import dataclasses
+
+        layers = 32
+        blocks = []
+        for i in range(layers):
+            sp = dataclasses.replace(spec, tokens=tokens, router_bias="zipf", seed=1000 + i)
+            blocks.append(b200_block(syn.make_case_on_device(sp, dev), regime=args.regime, device=dev))
+        block = blocks[0]
+        stack = B200MoeStack(blocks)
+        h = device_input(case, dev).reshape(tokens, spec.hidden).contiguous()
+        step = lambda: stack(h)
+        launches_per_step = 6 * layers
+    elif world == 1:
         block = b200_block(case, regime=args.regime, device=dev)
         h = device_input(case, dev).reshape(tokens, spec.hidden).contiguous()
         step = lambda: block(h)
@@ -229,7 +256,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
-    value = tokens / (ms_step * 1e-3)
+    value = tokens * layers / (ms_step * 1e-3)
     moe.device_status()
 
     # ---- same K steps again with CUDA events around every stage (the events
@@ -267,7 +294,26 @@ def main():
 
     # ---- end to end through the C ABI with host buffers (pinned), copies timed
     e2e = None
-    if world == 1:
+    if world == 1 and layers > 1:
+        hp = h.cpu().pin_memory()
+        yp = torch.empty_like(hp).pin_memory()
+        h_dev = torch.empty_like(h)
+        nbytes = hp.numel() * hp.element_size()
+
+        def e2e_step():
+            h_dev.copy_(hp, non_blocking=True)
+            yp.copy_(stack(h_dev), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        dt = time.perf_counter() - t0
+        e2e = {"value": tokens * layers * args.steps / dt, "unit": "tokens/s",
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+    elif world == 1:
         layer = block.layer
         hp = h.cpu().pin_memory()
         yp = torch.empty_like(hp).pin_memory()
@@ -338,8 +384,8 @@ def main():
                         "unit": "GB/s", "frac": ach / peak, "traffic": None,
                         "peak_source": peaks["source"] + " (copy)"}
         layer_bytes = experts_active * w_bytes_expert + 2 * tokens * spec.hidden * 2 + spec.experts * spec.hidden * 4
-        whole = {"tensor_frac": flops / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
-                 "hbm_frac": layer_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        whole = {"tensor_frac": layers * flops / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                 "hbm_frac": layers * layer_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     else:
         # gate/up kernel on every rank: flops of the rows each rank received over
         # the slowest rank's mean kernel time, against N x the single-GPU peak
@@ -376,11 +422,13 @@ def main():
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 operands (exact Q8_0 dequant), f32 accumulate, bf16 activations in/out",
             "data": "synthetic",
-            "config": {"workload": args.workload, "layer": "mixtral-8x7b MoE FFN, Q8_0 experts",
+            "config": {"workload": args.workload,
+                       "layer": f"{spec_name} MoE FFN ({spec.kind} experts, {spec.activation})"
+                                + (f", stack of {layers} layers, value = layer-tokens/s" if layers > 1 else ""),
                        "tokens": tokens, "hidden": spec.hidden, "ffn": spec.ffn,
                        "experts": spec.experts, "top_k": spec.top_k, "regime": args.regime,
                        "parallelism": "single GPU" if world == 1 else f"ep{world}",
-                       "l2": "weights (1.5 GB) exceed L2 (126 MB); no flush"},
+                       "l2": "expert weights (>= 0.8 GB per layer) exceed L2 (126 MB); no flush"},
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks, "roofline": roofline, "stage_ms": stage, "whole_layer": whole,
             "cpu_baseline": cpu,

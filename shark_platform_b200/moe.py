@@ -327,6 +327,21 @@ class B200MoeBlock(torch.nn.Module):
         return torch.ops.b200moe.layer_forward(h, self._handle, self.regime)
 
 
+class B200MoeStack(torch.nn.Module):
+    """Several MoE layers applied back to back (the MoE halves of consecutive
+    transformer blocks, without the attention in between): the output of layer i
+    is the input of layer i+1."""
+
+    def __init__(self, blocks):
+        super().__init__()
+        self.blocks = torch.nn.ModuleList(blocks)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        for blk in self.blocks:
+            h = blk(h)
+        return h
+
+
 # ------------------------------------------------------ op-level overrides
 class GatheredExperts:
     """What `ffn_*_exps.weight[experts, :, :]` returns for a quantized tensor: a

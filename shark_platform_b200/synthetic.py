@@ -218,3 +218,33 @@ def case_block(case: Case, regime: str = "auto", device="cuda"):
 def case_input(case: Case, device="cuda") -> torch.Tensor:
     h = case.h.to(device)
     return h.to(torch.bfloat16) if case.spec.act_dtype == "bf16" else h
+
+
+def make_case_on_device(spec: CaseSpec, device="cuda", seed: Optional[int] = None) -> Case:
+    """Same distributions as `make_case`, drawn with the device generator.  For
+    benchmarks that need tens of gigabytes of distinct weights (the 32-layer
+    stack); values differ from the CPU-seeded case of the same seed."""
+    T, d, f, e = spec.tokens, spec.hidden, spec.ffn, spec.experts
+    gen = torch.Generator(device=device).manual_seed(spec.seed if seed is None else seed)
+    rn = lambda *shape: torch.randn(*shape, generator=gen, device=device)
+    h = rn(1, T, d)
+    if spec.act_dtype == "bf16":
+        h = h.to(torch.bfloat16).to(torch.float32)
+    router_w = rn(e, d) * 0.02
+    router_b = None
+    if spec.router_bias == "zipf":
+        rank = torch.randperm(e, generator=gen, device=device) + 1
+        router_b = -1.2 * torch.log(rank.to(torch.float32))
+    elif spec.router_bias == "normal":
+        router_b = rn(e) * 0.5
+    norm_w = torch.ones(d, device=device)
+    out_norm_w = torch.ones(d, device=device) if spec.out_norm else None
+    if spec.kind != Q8_0:
+        raise NotImplementedError("device-side generation is implemented for Q8_0 only")
+
+    def planes(n, k):
+        qs = torch.randint(-127, 128, (e, n, k // 32, 32), generator=gen, device=device, dtype=torch.int8)
+        dd = (rn(e, n, k // 32, 1).abs() * 0.002).to(torch.float16)
+        return {"d": dd, "qs": qs}
+
+    return Case(spec, h, norm_w, router_w, router_b, out_norm_w, planes(f, d), planes(f, d), planes(d, f))

@@ -294,3 +294,32 @@ def test_stream_kernel_scale_paths_agree(M):
     b = M.grouped_matmul(xs, plan.seg_offsets, w_rows, tokens, C.REGIME_STREAM)
     assert torch.equal(a, b)
     assert M.device_status() == 0
+
+
+def test_stack_of_layers_with_zipf_router_bias(M):
+    """Three layers back to back, each with its own weights and a Zipf(1.2)
+    router bias (skewed routing); the oracle chains the same three layers."""
+    from shark_platform_b200.moe import B200MoeStack
+
+    blocks, params = [], []
+    h0 = None
+    for i in range(3):
+        spec = syn.CaseSpec(f"stack{i}", 64, 256, 512, kind=syn.Q8_0, router_bias="zipf",
+                            seed=500 + i, act_dtype="f32")
+        case = syn.make_case(spec)
+        # keep the residual stream at unit scale like a real model's norm-ed blocks
+        for planes in (case.down,):
+            planes["d"] = (planes["d"].float() * 0.05).half()
+        if h0 is None:
+            h0 = case.h
+        blocks.append(b200_block(case))
+        params.append(oracle_params(case))
+    want = h0
+    counts = torch.zeros(8)
+    for p in params:
+        want, mid = orc.moe_block(want, p, form="per_expert")
+        counts += torch.bincount(mid["experts"].reshape(-1), minlength=8)
+    assert counts.max() > 2.0 * counts.min(), "the Zipf bias should skew the routing"
+    y = B200MoeStack(blocks)(h0.cuda()).cpu()
+    assert M.device_status() == 0
+    assert orc.rel_l2(y, want) < REL_L2_TOL
