@@ -194,7 +194,14 @@ def main():
     from shark_platform_b200 import _cabi as C, moe, synthetic as syn
     b200_block, device_input = syn.case_block, syn.case_input
     spec = syn.CASES[spec_name]
-    case = syn.make_case(spec, tokens=tokens)
+    if world > 1:
+        # every rank draws the same full layer on its own GPU (same seed, same
+        # generator) and keeps its expert shard: seconds instead of a minute of
+        # host-side generation per rank
+        import dataclasses
+        case = syn.make_case_on_device(dataclasses.replace(spec, tokens=tokens), dev)
+    else:
+        case = syn.make_case(spec, tokens=tokens)
     peaks = measured_peaks()
     flops = syn.layer_flops(tokens, spec.top_k, spec.hidden, spec.ffn)
     w_bytes_expert = 3 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
