@@ -25,7 +25,6 @@ namespace {
 constexpr int CONSUMER_WARPS = 8;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int KT = 256;   // reduction elements per stage
-constexpr int SET_ROWS = 64;
 constexpr int MAX_E = 64;
 
 struct StreamArgs {
@@ -55,8 +54,15 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
       : "memory");
 }
 
-template <int LAYOUT, int S>
+// RW = row warps per k half: 4 (64 rows per set, two k halves, 8 consumer warps)
+// or 7 (112 rows per set, one k pass, 7 consumer warps): 112-row tiles divide
+// ffn sizes with a factor 7 (14336 = 128 x 112) into a number of work items
+// that fills the last wave of SMs.
+template <int LAYOUT, int S, int RW>
 struct Cfg {
+  static constexpr int SET_ROWS = 16 * RW;
+  static constexpr int KH = RW == 4 ? 2 : 1;   // k halves handled by different warps
+  static constexpr int ACTIVE = RW * KH;       // consumer warps that work
   static constexpr int MT = 8 * S;  // tokens per chunk
   // bytes of one row set of quantised values per stage
   static constexpr int WSET = LAYOUT == B200MOE_LAYOUT_Q8_0   ? SET_ROWS * KT
@@ -68,7 +74,7 @@ struct Cfg {
   static constexpr int XBOX = MT * 128;
   static constexpr int OFF_X = 2 * WSET;
   static constexpr int OFF_S = OFF_X + 4 * XBOX;
-  static constexpr int STAGE = OFF_S + 2 * SSET;
+  static constexpr int STAGE = (OFF_S + 2 * SSET + 1023) / 1024 * 1024;
   static constexpr int RED_FLOATS = 8 * S < 32 ? 8 * S : 32;  // floats per thread per reduce round
   static constexpr int RED_BYTES = 128 * RED_FLOATS * 4;
   static constexpr int BUDGET = 232448 - 1024 - RED_BYTES - 256;
@@ -86,15 +92,18 @@ __device__ __forceinline__ __half2 bcast_half(uint32_t v, int sel) {
   return u32_as_h2(__byte_perm(v, v, sel ? 0x3232 : 0x1010));
 }
 
-template <int LAYOUT, int NMAT, int S>
+template <int LAYOUT, int NMAT, int S, int RW>
 __global__ void __launch_bounds__(THREADS, 1)
 stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                    const __grid_constant__ CUtensorMap tm_s0, const __grid_constant__ CUtensorMap tm_s1,
                    const __grid_constant__ CUtensorMap tm_x8, const __grid_constant__ CUtensorMap tm_x16,
                    const __grid_constant__ CUtensorMap tm_x32, const __grid_constant__ CUtensorMap tm_x64,
                    const StreamArgs args) {
-  using C = Cfg<LAYOUT, S>;
+  using C = Cfg<LAYOUT, S, RW>;
   constexpr int STAGES = C::STAGES;
+  constexpr int SET_ROWS = C::SET_ROWS;
+  constexpr int KH = C::KH;
+  constexpr int SPANS = 4 / KH;  // 64-k spans of a stage per warp
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_seg[MAX_E + 1];
   __shared__ int s_prefix[MAX_E + 1];
@@ -113,7 +122,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
     s_exit = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), CONSUMER_WARPS);
+      mbar_init(empty_bar(s), C::ACTIVE);
     }
     fence_mbar_init();
     int run = 0;
@@ -206,7 +215,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
   }
 
   // -------------------------------------------------------------- consumers
-  const int w = warp & 3, kh = warp >> 2;
+  if (warp >= C::ACTIVE) return;  // RW = 7 leaves one consumer warp without rows
+  const int w = warp % RW, kh = warp / RW;
   const int g = lane >> 2, t = lane & 3;
   const int rg = rho(g);
   const int ctid = tid & 127;  // index within a k-half group
@@ -239,8 +249,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
           lds128(srow + 8 * 16, sc[r][1]);
         }
 #pragma unroll
-        for (int spi = 0; spi < 2; ++spi) {
-          const int sp = 2 * kh + spi;  // 64-k span of the stage
+        for (int spi = 0; spi < SPANS; ++spi) {
+          const int sp = SPANS * kh + spi;  // 64-k span of the stage
           const int cb = (sp & 1) * 4;
           uint32_t alo[2][2][4], ahi[2][2][4];
 #pragma unroll
@@ -251,7 +261,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
             for (int hf = 0; hf < 2; ++hf) {
               uint32_t q[4];
               lds128(wbase + hf * 8 * 128, q);
-              const uint32_t sw = kh ? sc[r][hf][2 + spi] : sc[r][hf][spi];
+              const uint32_t sw = (KH == 2 && kh) ? sc[r][hf][(2 + spi) & 3] : sc[r][hf][spi];
               const __half2 scale = bcast_half(sw, t >> 1);
 #pragma unroll
               for (int j = 0; j < 4; ++j) dequant_q8x4(q[j], scale, alo[r][hf][j], ahi[r][hf][j]);
@@ -277,8 +287,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
         // dense fp16 weights: one 128-byte box per 64-k span, fragments are the
         // staged values themselves
 #pragma unroll
-        for (int spi = 0; spi < 2; ++spi) {
-          const int sp = 2 * kh + spi;
+        for (int spi = 0; spi < SPANS; ++spi) {
+          const int sp = SPANS * kh + spi;
           uint32_t a[2][2][8];
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
@@ -310,8 +320,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
         // Q4_K: one 128-byte box row = 256 k = one super-block; a 64-k span is
         // 32 bytes; thread t owns 8 bytes = 16 quants of sub-block 2*sp + (t>>1).
 #pragma unroll
-        for (int spi = 0; spi < 2; ++spi) {
-          const int sp = 2 * kh + spi;
+        for (int spi = 0; spi < SPANS; ++spi) {
+          const int sp = SPANS * kh + spi;
           uint32_t a[2][2][4][2];  // [set][row half][mma j][lo,hi]
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
@@ -359,29 +369,33 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
       if (lane == 0) mbar_arrive(empty_bar(slot));
     }
 
-    // ---- add the two k halves: kh=1 warps hand their sums to kh=0 warps
-    constexpr int TOTAL = 8 * S;
-    constexpr int ROUNDS = TOTAL / C::RED_FLOATS;
-    float* accf = &acc[0][0][0];
-    float* red = reinterpret_cast<float*>(smem_raw + (red_base - smem_u32(smem_raw)));
+    if constexpr (KH == 2) {
+      // ---- add the two k halves: kh=1 warps hand their sums to kh=0 warps
+      constexpr int TOTAL = 8 * S;
+      constexpr int ROUNDS = TOTAL / C::RED_FLOATS;
+      float* accf = &acc[0][0][0];
+      float* red = reinterpret_cast<float*>(smem_raw + (red_base - smem_u32(smem_raw)));
 #pragma unroll
-    for (int rd = 0; rd < ROUNDS; ++rd) {
-      if (kh == 1) {
+      for (int rd = 0; rd < ROUNDS; ++rd) {
+        if (kh == 1) {
 #pragma unroll
-        for (int i = 0; i < C::RED_FLOATS; ++i) red[i * 128 + ctid] = accf[rd * C::RED_FLOATS + i];
+          for (int i = 0; i < C::RED_FLOATS; ++i) red[i * 128 + ctid] = accf[rd * C::RED_FLOATS + i];
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (kh == 0) {
+#pragma unroll
+          for (int i = 0; i < C::RED_FLOATS; ++i) accf[rd * C::RED_FLOATS + i] += red[i * 128 + ctid];
+          // one thread decides for all consumers whether the CTA gives up, so
+          // that every warp leaves the item loop at the same barrier
+          if (rd == ROUNDS - 1 && ctid == 0) s_exit = *abort_flag;
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (kh == 0) {
-#pragma unroll
-        for (int i = 0; i < C::RED_FLOATS; ++i) accf[rd * C::RED_FLOATS + i] += red[i * 128 + ctid];
-        // one thread decides for all consumers whether the CTA gives up, so
-        // that every warp leaves the item loop at the same barrier
-        if (rd == ROUNDS - 1 && ctid == 0) s_exit = *abort_flag;
-      }
-      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (s_exit) break;
+      if (kh != 0) continue;
+    } else {
+      if (*abort_flag) break;  // no barriers between consumer warps in this geometry
     }
-    if (s_exit) break;
-    if (kh != 0) continue;
 
     // ---- epilogue
     const int seg_end = row0 + rows;
@@ -412,10 +426,10 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
   }
 }
 
-template <int LAYOUT, int NMAT, int S>
+template <int LAYOUT, int NMAT, int S, int RW>
 int launch_t(const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
-  using C = Cfg<LAYOUT, S>;
-  auto kern = stream_gemm_kernel<LAYOUT, NMAT, S>;
+  using C = Cfg<LAYOUT, S, RW>;
+  auto kern = stream_gemm_kernel<LAYOUT, NMAT, S, RW>;
   static bool configured[16] = {};
   int dev = 0;
   B200_CHECK_CUDA(cudaGetDevice(&dev));
@@ -429,17 +443,17 @@ int launch_t(const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
   return B200MOE_OK;
 }
 
-template <int LAYOUT, int NMAT>
+template <int LAYOUT, int NMAT, int RW>
 int launch_s(int S, const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
   switch (S) {
-    case 1: return launch_t<LAYOUT, NMAT, 1>(maps, a, st);
-    case 2: return launch_t<LAYOUT, NMAT, 2>(maps, a, st);
-    case 4: return launch_t<LAYOUT, NMAT, 4>(maps, a, st);
-    default: return launch_t<LAYOUT, NMAT, 8>(maps, a, st);
+    case 1: return launch_t<LAYOUT, NMAT, 1, RW>(maps, a, st);
+    case 2: return launch_t<LAYOUT, NMAT, 2, RW>(maps, a, st);
+    case 4: return launch_t<LAYOUT, NMAT, 4, RW>(maps, a, st);
+    default: return launch_t<LAYOUT, NMAT, 8, RW>(maps, a, st);
   }
 }
 
-int weight_maps(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts) {
+int weight_maps(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts, int SET_ROWS = 64) {
   const uint64_t rows = static_cast<uint64_t>(w->experts) * w->rows;
   if (w->layout == B200MOE_LAYOUT_Q8_0) {
     if (int rc = make_tmap_2d(tw, w->qs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, w->cols, SET_ROWS,
@@ -516,17 +530,34 @@ int launch_stream_gate_up(const void* xs, const int32_t* seg, int pairs, int max
   B200_REQUIRE(gate->layout == up->layout && gate->rows == up->rows && gate->cols == up->cols &&
                    gate->experts == up->experts,
                "stream kernel: gate and up must have the same layout and shape");
-  B200_REQUIRE(gate->rows % SET_ROWS == 0, "stream kernel: ffn (%d) must be a multiple of 64",
-               gate->rows);
+  B200_REQUIRE(gate->rows % 64 == 0, "stream kernel: ffn (%d) must be a multiple of 64", gate->rows);
   if (pairs == 0) return B200MOE_OK;
-  const int S = pick_s(max_segment);
+  int S = pick_s(max_segment);
+  // Tile height: 64 rows per set, or 112 where that fills the last wave of SMs
+  // better (e.g. ffn 14336: 1792 items = 12.1 waves vs 1024 items = 6.9 waves).
+  // The 112-row geometry has room for 16-token chunks only; longer segments are
+  // processed in several chunks, so it is used for short segments only.
+  int set_rows = 64;
+  if (gate->layout == B200MOE_LAYOUT_Q8_0 && gate->rows % 112 == 0 && max_segment <= 32) {
+    const double sms = sm_count();
+    const int active = pairs < gate->experts ? pairs : gate->experts;
+    auto eff = [&](int rows) {
+      const double items = static_cast<double>(active) * (gate->rows / rows);
+      const double waves = (items + sms - 1) / sms;
+      return items / (static_cast<long long>(waves) * sms);
+    };
+    if (eff(112) > eff(64) + 0.02) {
+      set_rows = 112;
+      if (S > 2) S = 2;
+    }
+  }
   CUtensorMap maps[8];
-  if (int rc = weight_maps(gate, &maps[0], &maps[2])) return rc;
-  if (int rc = weight_maps(up, &maps[1], &maps[3])) return rc;
+  if (int rc = weight_maps(gate, &maps[0], &maps[2], set_rows)) return rc;
+  if (int rc = weight_maps(up, &maps[1], &maps[3], set_rows)) return rc;
   if (int rc = token_maps(maps, xs, pairs, static_cast<uint64_t>(gate->cols) * 2, S)) return rc;
   StreamArgs a{};
   a.seg = seg; a.E = gate->experts; a.N = gate->rows; a.K = gate->cols;
-  a.ntiles = gate->rows / SET_ROWS; a.ksplit = 1; a.stages_per_item = gate->cols / KT;
+  a.ntiles = gate->rows / set_rows; a.ksplit = 1; a.stages_per_item = gate->cols / KT;
   a.P = pairs; a.act = act; a.out_kperm = out_kperm; a.out = a_out; a.status = device_status_ptr();
   if (gate->layout == B200MOE_LAYOUT_Q8_0 && gate->sub != nullptr && up->sub != nullptr) {
     a.st0 = static_cast<const uint8_t*>(gate->sub);
@@ -534,15 +565,19 @@ int launch_stream_gate_up(const void* xs, const int32_t* seg, int pairs, int max
   }
   a.total_rows = static_cast<long long>(gate->experts) * gate->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
-  if (gate->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 2>(S, maps, a, st);
-  if (gate->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 2>(S, maps, a, st);
-  return launch_s<B200MOE_LAYOUT_Q4_K, 2>(S, maps, a, st);
+  if (set_rows == 112) {
+    return S == 1 ? launch_t<B200MOE_LAYOUT_Q8_0, 2, 1, 7>(maps, a, st)
+                  : launch_t<B200MOE_LAYOUT_Q8_0, 2, 2, 7>(maps, a, st);
+  }
+  if (gate->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 2, 4>(S, maps, a, st);
+  if (gate->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 2, 4>(S, maps, a, st);
+  return launch_s<B200MOE_LAYOUT_Q4_K, 2, 4>(S, maps, a, st);
 }
 
 int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_segment,
                        const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st) {
   if (int rc = check_weight(down, "down")) return rc;
-  B200_REQUIRE(down->rows % (2 * SET_ROWS) == 0,
+  B200_REQUIRE(down->rows % 128 == 0,
                "stream kernel: hidden (%d) must be a multiple of 128", down->rows);
   B200_REQUIRE(ksplit >= 1 && (down->cols / KT) % ksplit == 0, "stream kernel: bad k split %d",
                ksplit);
@@ -555,16 +590,16 @@ int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_
   if (int rc = token_maps(maps, a_in, pairs, static_cast<uint64_t>(down->cols) * 2, S)) return rc;
   StreamArgs a{};
   a.seg = seg; a.E = down->experts; a.N = down->rows; a.K = down->cols;
-  a.ntiles = down->rows / (2 * SET_ROWS); a.ksplit = ksplit;
+  a.ntiles = down->rows / 128; a.ksplit = ksplit;
   a.stages_per_item = down->cols / KT / ksplit;
   a.P = pairs; a.act = 0; a.out_kperm = 0; a.out = d_out; a.status = device_status_ptr();
   if (down->layout == B200MOE_LAYOUT_Q8_0 && down->sub != nullptr)
     a.st0 = a.st1 = static_cast<const uint8_t*>(down->sub);
   a.total_rows = static_cast<long long>(down->experts) * down->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
-  if (down->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 1>(S, maps, a, st);
-  if (down->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 1>(S, maps, a, st);
-  return launch_s<B200MOE_LAYOUT_Q4_K, 1>(S, maps, a, st);
+  if (down->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 1, 4>(S, maps, a, st);
+  if (down->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 1, 4>(S, maps, a, st);
+  return launch_s<B200MOE_LAYOUT_Q4_K, 1, 4>(S, maps, a, st);
 }
 
 }  // namespace b200moe

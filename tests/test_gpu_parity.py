@@ -323,3 +323,23 @@ def test_stack_of_layers_with_zipf_router_bias(M):
     y = B200MoeStack(blocks)(h0.cuda()).cpu()
     assert M.device_status() == 0
     assert orc.rel_l2(y, want) < REL_L2_TOL
+
+
+@pytest.mark.parametrize("tokens,skew", [(1, False), (9, False), (32, False), (32, True)])
+def test_stream_kernel_112_row_tiles(M, tokens, skew):
+    """ffn 14336 = 128 x 112: the decode kernel picks 112-row tiles (7 row warps,
+    16-token chunks).  With a skewed router some experts get more than 16 rows
+    and are processed in two chunks."""
+    spec = syn.CaseSpec("rw7", tokens, 256, 14336, kind=syn.Q8_0, seed=700 + tokens, act_dtype="f32",
+                        router_bias="zipf" if skew else None)
+    case = syn.make_case(spec)
+    if skew:
+        case.router_b = case.router_b * 3.0
+    want, mid = orc.moe_block(case.h, oracle_params(case), form="per_expert")
+    if skew:
+        assert torch.bincount(mid["experts"].reshape(-1), minlength=8).max() > 16
+    blk = b200_block(case, regime="stream")
+    y, experts, _ = blk.layer.forward(case.h.cuda(), regime=M.REGIMES["stream"], want_routing=True)
+    assert M.device_status() == 0
+    assert torch.equal(experts.cpu().to(torch.int64), mid["experts"])
+    assert orc.rel_l2(y.cpu() - case.h, want - case.h) < REL_L2_TOL
