@@ -171,6 +171,8 @@ def main():
     ap.add_argument("--workload", default="prefill4096", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--regime", default="auto", choices=["auto", "stream", "tensor"])
+    ap.add_argument("--ep", default="p2p", choices=["p2p", "nccl"],
+                    help="token exchange between ranks: peer-to-peer stores or NCCL all-to-all")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     spec_name, tokens = WORKLOADS[args.workload]
@@ -230,7 +232,16 @@ def main():
     else:
         from shark_platform_b200 import parallel
 
-        block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime)
+        transport = args.ep
+        if transport == "p2p":
+            try:
+                block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime,
+                                                 transport="p2p")
+            except Exception as exc:  # symmetric memory not available on this machine
+                transport = f"nccl (p2p set-up failed: {type(exc).__name__}: {str(exc)[:120]})"
+                block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime)
+        else:
+            block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime)
         per = tokens // world
         h = device_input(case, dev).reshape(tokens, spec.hidden)[rank * per:(rank + 1) * per].contiguous()
         step = lambda: block(h)
@@ -398,7 +409,7 @@ def main():
         # the slowest rank's mean kernel time, against N x the single-GPU peak
         tm = block.backend.timings
         gu_ms = sum(ev[0].elapsed_time(ev[1]) for ev, _ in tm) / max(len(tm), 1)
-        rows = sum(n for _, n in tm) / max(len(tm), 1)
+        rows = sum((n if n >= 0 else tokens * spec.top_k / world) for _, n in tm) / max(len(tm), 1)
         t = torch.tensor([gu_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         r = torch.tensor([rows], device=dev)
@@ -434,7 +445,7 @@ def main():
                                 + (f", stack of {layers} layers, value = layer-tokens/s" if layers > 1 else ""),
                        "tokens": tokens, "hidden": spec.hidden, "ffn": spec.ffn,
                        "experts": spec.experts, "top_k": spec.top_k, "regime": args.regime,
-                       "parallelism": "single GPU" if world == 1 else f"ep{world}",
+                       "parallelism": "single GPU" if world == 1 else f"ep{world}, exchange: {transport}",
                        "l2": "expert weights (>= 0.8 GB per layer) exceed L2 (126 MB); no flush"},
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks, "roofline": roofline, "stage_ms": stage, "whole_layer": whole,

@@ -207,6 +207,44 @@ int b200moe_exchange_plan(const int32_t* counts, int32_t world, int32_t experts_
 int b200moe_gather_rows(const void* rows, const int32_t* idx, int32_t n, int32_t div,
                         int32_t row_bytes, void* out, void* stream);
 
+/* Peer-to-peer expert parallelism (no reference counterpart).  All pointer
+ * arrays are indexed by rank and hold addresses valid on THIS device: entry
+ * [rank] is the local buffer, the others are peer mappings of the same buffer
+ * on the other ranks (symmetric allocation).
+ *   counts_all  int32 [world][E]   row s = rank s's pair counts per global expert
+ *   flags       int32 [world]      barrier flags, zero before the first call
+ *   recv_x      fp16  [cap_rows][d] rows routed to this rank's experts
+ *   ret_y       bf16  [ret_rows][d] results for this rank's own pairs
+ * Sequence per layer on every rank: route + route_plan (all E experts) ->
+ * ep_publish_counts -> ep_barrier(epoch, seg2) -> ep_dispatch ->
+ * ep_barrier(epoch+1) -> gate_up/down on recv_x with seg2 -> ep_return ->
+ * ep_barrier(epoch+2) -> combine on ret_y (bf16) with the route plan's inv.
+ * Epochs must increase by one per barrier and be the same on all ranks.  Waits
+ * are bounded (about two seconds): a missing peer sets the device status word
+ * instead of hanging. */
+typedef struct {
+  int32_t world, rank, experts_local;
+  void* counts_all[16];
+  void* flags[16];
+  void* recv_x[16];
+  void* ret_y[16];
+} b200moe_ep_t;
+
+int b200moe_ep_publish_counts(const b200moe_ep_t* ep, const int32_t* counts, void* stream);
+/* seg2_out (optional): [experts_local+1] segment offsets of the rows this rank
+ * will receive, derived from the completed counts matrix. */
+int b200moe_ep_barrier(const b200moe_ep_t* ep, int32_t epoch, int32_t* seg2_out, void* stream);
+/* Pushes xn[perm[i]/top_k] for every sorted pair i into the owner's recv_x. */
+int b200moe_ep_dispatch(const b200moe_ep_t* ep, const void* xn, const int32_t* experts,
+                        const int32_t* perm, const int32_t* seg_offsets, int32_t pairs,
+                        int32_t top_k, int32_t hidden, int32_t kperm, int32_t cap_rows,
+                        void* stream);
+/* Pushes the rows of d_rows (fp32 [ksplit][cap_rows][d], grouped like recv_x)
+ * as bf16 into the source ranks' ret_y. */
+int b200moe_ep_return(const b200moe_ep_t* ep, const float* d_rows, int32_t ksplit,
+                      int32_t cap_rows, const int32_t* seg2, int32_t hidden, int32_t ret_rows,
+                      void* stream);
+
 /* Bytes of workspace b200moe_layer_forward needs for up to `tokens` tokens. */
 size_t b200moe_workspace_bytes(const b200moe_layer_t* layer, int32_t tokens);
 

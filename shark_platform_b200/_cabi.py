@@ -55,6 +55,18 @@ class LayerDesc(ctypes.Structure):
     ]
 
 
+class EpDesc(ctypes.Structure):
+    _fields_ = [
+        ("world", c_int32),
+        ("rank", c_int32),
+        ("experts_local", c_int32),
+        ("counts_all", c_void_p * 16),
+        ("flags", c_void_p * 16),
+        ("recv_x", c_void_p * 16),
+        ("ret_y", c_void_p * 16),
+    ]
+
+
 def declared_symbols() -> list[str]:
     """Names of every function the public header declares."""
     with open(HEADER_PATH) as f:
@@ -95,6 +107,10 @@ _PROTOS = {
     "b200moe_combine": (c_int, [_P, c_int, c_int32, c_int32, _P, _P, _P, c_int, c_int32, _L, c_int, _P, c_int, _P]),
     "b200moe_exchange_plan": (c_int, [_P, c_int32, c_int32, _P, _P, _P, _P]),
     "b200moe_gather_rows": (c_int, [_P, _P, c_int32, c_int32, c_int32, _P, _P]),
+    "b200moe_ep_publish_counts": (c_int, [POINTER(EpDesc), _P, _P]),
+    "b200moe_ep_barrier": (c_int, [POINTER(EpDesc), c_int32, _P, _P]),
+    "b200moe_ep_dispatch": (c_int, [POINTER(EpDesc), _P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32, _P]),
+    "b200moe_ep_return": (c_int, [POINTER(EpDesc), _P, c_int32, c_int32, _P, c_int32, c_int32, _P]),
     "b200moe_workspace_bytes": (c_size_t, [_L, c_int32]),
     "b200moe_layer_forward": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, c_size_t, _P, _P, _P]),
     "b200moe_layer_forward_host": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, _P, c_size_t, _P]),

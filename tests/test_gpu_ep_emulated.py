@@ -1,0 +1,82 @@
+"""Peer-to-peer dispatch / return index arithmetic with several emulated ranks on
+ONE GPU: every "rank" gets its own buffers on the same device and the kernels of
+all ranks run one after another (no kernel waits for another: the barrier kernel
+is not used here, its segment offsets are recomputed with torch)."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("world,E,k,tokens", [(2, 8, 2, 37), (4, 8, 2, 50), (8, 8, 2, 16), (2, 4, 1, 9)])
+def test_dispatch_and_return_round_trip(world, E, k, tokens):
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from shark_platform_b200 import _cabi as C, moe
+
+    d, el = 64, E // world
+    gen = torch.Generator().manual_seed(world * 100 + tokens)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    cap, ret_rows = tokens * world * min(k, el), tokens * k
+    counts_all = [torch.zeros(world, E, dtype=torch.int32, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
+    recv = [torch.zeros(cap, d, dtype=torch.float16, device="cuda") for _ in range(world)]
+    ret = [torch.zeros(ret_rows, d, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    eps = []
+    for r in range(world):
+        ep = C.EpDesc()
+        ep.world, ep.rank, ep.experts_local = world, r, el
+        for i in range(world):
+            ep.counts_all[i], ep.flags[i] = counts_all[i].data_ptr(), flags[i].data_ptr()
+            ep.recv_x[i], ep.ret_y[i] = recv[i].data_ptr(), ret[i].data_ptr()
+        eps.append(ep)
+    xs, exs, plans = [], [], []
+    for r in range(world):
+        # small integers (exact in fp16 and bf16): column 1 holds the rank, the others the token
+        x = (torch.arange(tokens).view(-1, 1) + torch.zeros(tokens, d))
+        x[:, 1] = r
+        x = x.to(torch.float16).cuda()
+        ex = torch.stack([torch.randperm(E, generator=gen)[:k] for _ in range(tokens)]).to(torch.int32).cuda()
+        plan = moe.route_plan(ex, E)
+        C.check(C.lib.b200moe_ep_publish_counts(ctypes.byref(eps[r]), p(plan.counts), st))
+        xs.append(x); exs.append(ex); plans.append(plan)
+    torch.cuda.synchronize()
+    full = torch.stack([pl.counts.cpu() for pl in plans])  # [src, E]
+    for r in range(world):
+        assert torch.equal(counts_all[r].cpu(), full)
+    for r in range(world):
+        C.check(C.lib.b200moe_ep_dispatch(ctypes.byref(eps[r]), p(xs[r]), p(exs[r]), p(plans[r].perm),
+                                          p(plans[r].seg_offsets), tokens * k, k, d, 0, cap, st))
+    torch.cuda.synchronize()
+    assert moe.device_status() == 0
+    seg2s = []
+    for q in range(world):
+        # expected receive buffer: experts ascending, then source ranks ascending, then the
+        # source's own stable order (ascending pair id)
+        want = []
+        seg2 = [0]
+        for e in range(el):
+            g = q * el + e
+            for src in range(world):
+                pairs = torch.nonzero(exs[src].reshape(-1).cpu() == g).reshape(-1)
+                want += [(float(int(pp) // k), float(src)) for pp in pairs]
+            seg2.append(len(want))
+        got = [tuple(v) for v in recv[q][:len(want), 0:2].float().cpu().tolist()]
+        assert got == want, (q, got[:8], want[:8])
+        seg2s.append(torch.tensor(seg2, dtype=torch.int32, device="cuda"))
+    # "expert computation": result row = 2 * input row, as fp32 in two k-split halves
+    for q in range(world):
+        dpart = torch.stack([recv[q].float() * 1.5, recv[q].float() * 0.5])
+        C.check(C.lib.b200moe_ep_return(ctypes.byref(eps[q]), p(dpart), 2, cap, p(seg2s[q]), d, ret_rows, st))
+        torch.cuda.synchronize()
+    assert moe.device_status() == 0
+    for r in range(world):
+        # ret_y is in rank r's expert-sorted order: position i holds pair perm[i]
+        perm = plans[r].perm.cpu().long()
+        want = 2.0 * (perm // k).float()
+        assert torch.equal(ret[r][:tokens * k, 0].float().cpu(), want)
+        assert torch.equal(ret[r][:tokens * k, -1].float().cpu(), want)
+        assert torch.equal(ret[r][:tokens * k, 1].float().cpu(), torch.full_like(want, 2.0 * r))

@@ -21,7 +21,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, name, tokens, regime, out):
+def _worker(rank, world, port, name, tokens, regime, out, transport="nccl"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -32,7 +32,8 @@ def _worker(rank, world, port, name, tokens, regime, out):
 
         spec = syn.CASES[name]
         case = syn.make_case(spec, tokens=tokens)
-        block = parallel.build_from_case(case, regime=regime)
+        block = parallel.build_from_case(case, regime=regime, transport=transport,
+                                         max_local_tokens=tokens)
         per = tokens // world
         full = case.h.reshape(tokens, spec.hidden)
         lo, hi = rank * per, (tokens if rank == world - 1 else (rank + 1) * per)
@@ -40,7 +41,9 @@ def _worker(rank, world, port, name, tokens, regime, out):
         if spec.act_dtype == "bf16":
             h = h.to(torch.bfloat16)
         y = block(h).float().cpu()
+        y2 = block(h).float().cpu()  # second call: buffers and barrier epochs are reused
         torch.cuda.synchronize()
+        assert torch.equal(y, y2)
         assert moe.device_status() == 0
         want, _ = orc.moe_block(case.h, oracle_params(case), form="per_expert")
         out[rank] = orc.rel_l2(y, want.reshape(tokens, spec.hidden)[lo:hi])
@@ -57,5 +60,19 @@ def test_expert_parallel_two_gpus(name, tokens, regime):
     with mp.Manager() as mgr:
         out = mgr.dict()
         mp.spawn(_worker, args=(world, _free_port(), name, tokens, regime, out), nprocs=world, join=True)
+        for r in range(world):
+            assert out[r] < 2e-2, (r, out[r])
+
+
+@pytest.mark.parametrize("name,tokens,regime", [("small_q8", 40, "auto"), ("small_q4k", 33, "auto"),
+                                                ("small_grok", 300, "tensor")])
+def test_expert_parallel_two_gpus_peer_to_peer(name, tokens, regime):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(world, _free_port(), name, tokens, regime, out, "p2p"),
+                 nprocs=world, join=True)
         for r in range(world):
             assert out[r] < 2e-2, (r, out[r])
