@@ -152,7 +152,9 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
                     const b200moe_weight_t* up, int activation, int regime, int32_t out_kperm,
                     void* a_out, void* stream);
 
-/* Number of k-split partial sums b200moe_down writes for these arguments. */
+/* Number of k-split partial sums the down projection should use.  `pairs` is the
+ * number of rows expected (an estimate is fine: it only steers load balance);
+ * pass the result to b200moe_down and size d_out with it. */
 int b200moe_down_ksplit(const b200moe_weight_t* down, int32_t pairs, int32_t max_segment,
                         int regime);
 
@@ -161,7 +163,8 @@ int b200moe_down_ksplit(const b200moe_weight_t* down, int32_t pairs, int32_t max
  * [pairs,F]; d_out fp32 [ksplit, pairs, d] partial sums with ksplit =
  * b200moe_down_ksplit(...) (the combine adds the partials in index order). */
 int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32_t max_segment,
-                 const b200moe_weight_t* down, int regime, float* d_out, void* stream);
+                 const b200moe_weight_t* down, int regime, int32_t ksplit, float* d_out,
+                 void* stream);
 
 /* No counterpart in the reference.  The same down projection as b200moe_down
  * for hosts that cannot allocate device memory where they call the layer (an

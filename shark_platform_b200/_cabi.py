@@ -102,7 +102,7 @@ _PROTOS = {
     "b200moe_kperm": (c_int, [c_int, c_int, c_int32]),
     "b200moe_gate_up": (c_int, [_P, _P, c_int32, c_int32, _W, _W, c_int, c_int, c_int32, _P, _P]),
     "b200moe_down_ksplit": (c_int, [_W, c_int32, c_int32, c_int]),
-    "b200moe_down": (c_int, [_P, _P, c_int32, c_int32, _W, c_int, _P, _P]),
+    "b200moe_down": (c_int, [_P, _P, c_int32, c_int32, _W, c_int, c_int32, _P, _P]),
     "b200moe_down_noalloc": (c_int, [_P, _P, c_int32, c_int32, _W, _P, _P]),
     "b200moe_combine": (c_int, [_P, c_int, c_int32, c_int32, _P, _P, _P, c_int, c_int32, _L, c_int, _P, c_int, _P]),
     "b200moe_exchange_plan": (c_int, [_P, c_int32, c_int32, _P, _P, _P, _P]),

@@ -154,7 +154,8 @@ Workspace carve(const b200moe_layer_t* L, int tokens, void* base) {
   const size_t T = tokens > 0 ? tokens : 1;
   const size_t P = T * L->top_k;
   const size_t d = L->hidden, F = L->ffn;
-  const int ks = stream_down_ksplit(&L->down, static_cast<int>(P));  // >= the tensor regime's 1
+  int ks = stream_down_ksplit(&L->down, static_cast<int>(P));
+  if (tc_supported(&L->down)) ks = max(ks, tc_down_ksplit(&L->down, static_cast<int>(P)));
   uint8_t* p = static_cast<uint8_t*>(base);
   size_t off = 0;
   auto take = [&](size_t n) {
@@ -321,19 +322,22 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
 int b200moe_down_ksplit(const b200moe_weight_t* down, int32_t pairs, int32_t max_segment,
                         int regime) {
   if (down == nullptr) return 1;
-  if (pick_regime(regime, down, max_segment) == B200MOE_REGIME_TENSOR) return 1;
+  if (pick_regime(regime, down, max_segment) == B200MOE_REGIME_TENSOR)
+    return tc_down_ksplit(down, pairs);
   return stream_down_ksplit(down, pairs);
 }
 
 int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32_t max_segment,
-                 const b200moe_weight_t* down, int regime, float* d_out, void* stream) {
+                 const b200moe_weight_t* down, int regime, int32_t ksplit, float* d_out,
+                 void* stream) {
   B200_REQUIRE(down && seg_offsets, "down: NULL argument");
   B200_REQUIRE(pairs == 0 || (a && d_out), "down: NULL buffer");
+  B200_REQUIRE(ksplit >= 1, "down: ksplit must come from b200moe_down_ksplit");
   const int r = pick_regime(regime, down, max_segment);
   if (r == B200MOE_REGIME_TENSOR)
-    return launch_tc_down(a, seg_offsets, pairs, 192, down, d_out, static_cast<cudaStream_t>(stream));
-  return launch_stream_down(a, seg_offsets, pairs, max_segment, down,
-                            stream_down_ksplit(down, pairs), d_out,
+    return launch_tc_down(a, seg_offsets, pairs, 192, down, ksplit, d_out,
+                          static_cast<cudaStream_t>(stream));
+  return launch_stream_down(a, seg_offsets, pairs, max_segment, down, ksplit, d_out,
                             static_cast<cudaStream_t>(stream));
 }
 
@@ -402,7 +406,7 @@ int b200moe_layer_forward(const b200moe_layer_t* L, const void* h, void* y, int 
     return rc;
   prof_mark(pc, 4, st);
   const int ks = b200moe_down_ksplit(&L->down, pairs, tokens, regime);
-  if (int rc = b200moe_down(w.a, w.seg, pairs, tokens, &L->down, regime, w.dpart, stream)) return rc;
+  if (int rc = b200moe_down(w.a, w.seg, pairs, tokens, &L->down, regime, ks, w.dpart, stream)) return rc;
   prof_mark(pc, 5, st);
   if (int rc = launch_combine(w.dpart, B200MOE_DT_F32, ks, pairs, w.inv, w.gates, h, io_dtype,
                               tokens, L, 1, y, io_dtype, st))

@@ -40,7 +40,8 @@ bool tc_supported(const b200moe_weight_t* w);
 int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_tile,
                       const b200moe_weight_t* gate, const b200moe_weight_t* up, int act,
                       int out_kperm, void* a_out, cudaStream_t st);
+int tc_down_ksplit(const b200moe_weight_t* down, int est_pairs);
 int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile,
-                   const b200moe_weight_t* down, float* d_out, cudaStream_t st);
+                   const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st);
 
 }  // namespace b200moe

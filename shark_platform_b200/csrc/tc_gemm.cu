@@ -72,6 +72,7 @@ struct TcArgs {
   int E, N, K;
   int ntiles;      // row tiles per expert (N / 128 for gate+up, N / 256 for down)
   int tok_tile;    // upper bound on tokens per tile (multiple of 16, <= 192)
+  int ksplit;      // k partitions per tile (down only); partial kc goes to out + kc*P*N
   int P;
   int act;
   int out_kperm;   // gate/up only: interleave output columns for a Q4_K down matrix
@@ -223,7 +224,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       const int a = args.seg[e], b = args.seg[e + 1];
       s_seg[e] = a;
       s_prefix[e] = run;
-      run += ((b - a + args.tok_tile - 1) / args.tok_tile) * args.ntiles;
+      run += ((b - a + args.tok_tile - 1) / args.tok_tile) * args.ntiles * args.ksplit;
     }
     s_seg[args.E] = args.seg[args.E];
     s_prefix[args.E] = run;
@@ -238,12 +239,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   const uint32_t tmem = s_tmem;
   const int total_tiles = s_prefix[args.E];
   volatile int* abort_flag = &s_abort;
-  const int stages_per_tile = args.K / TC_KT;  // a multiple of 4
+  const int stages_per_tile = args.K / TC_KT / args.ksplit;  // a multiple of 4
   constexpr bool Q4 = LAYOUT == B200MOE_LAYOUT_Q4_K;
   constexpr uint32_t WSET_BYTES = Q4 ? TC_ROWS * 64 : TC_ROWS * 128;  // one set, 128 k
   constexpr uint32_t SSET_BYTES = Q4 ? TC_ROWS * 32 : TC_ROWS * 16;   // one set, 256 k
 
-  // tile -> (expert, row tile, first token row, token rows, MMA N)
+  // tile -> (expert, row tile | k partition << 16, first token row, token rows, MMA N)
   auto decode = [&](int tile, int& e, int& nt, int& row0, int& rows, int& ncols) {
     e = 0;
     while (tile >= s_prefix[e + 1]) ++e;
@@ -251,7 +252,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int m = s_seg[e + 1] - s_seg[e];
     const int mtiles = (m + args.tok_tile - 1) / args.tok_tile;
     const int mt = local % mtiles;
-    nt = local / mtiles;
+    const int rest = local / mtiles;
+    nt = (rest / args.ksplit) | ((rest % args.ksplit) << 16);
     const int per = ((m + mtiles - 1) / mtiles + 15) & ~15;  // balanced, multiple of 16
     row0 = s_seg[e] + mt * per;
     rows = min(per, s_seg[e + 1] - row0);
@@ -267,10 +269,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int e, nt, row0, rows, ncols;
         decode(tile, e, nt, row0, rows, ncols);
+        const int kbase = (nt >> 16) * stages_per_tile * TC_KT;
+        nt &= 0xffff;
         const int grow0 = e * args.N + nt * (NMAT == 2 ? TC_ROWS : 2 * TC_ROWS);
         const int grow1 = NMAT == 2 ? grow0 : grow0 + TC_ROWS;
         for (int st = 0; st < stages_per_tile; st += 2, n += 2) {
-          const int k0 = st * TC_KT;
+          const int k0 = kbase + st * TC_KT;
           if (st % TC_SGROUP == 0) {
             const uint32_t g = n / TC_SGROUP;
             const int ss = g % TC_SSLOTS;
@@ -327,7 +331,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           if (!mbar_wait(xempty + 8u * xs, ((n / TC_XSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
           const uint32_t xb = xfull + 8u * xs;
           mbar_expect_tx(xb, xbytes);
-          tma_load_2d(x_base + xs * TC_XSLOT, tx, st * TC_KT * 2, row0, xb);
+          tma_load_2d(x_base + xs * TC_XSLOT, tx, ((nt >> 16) * stages_per_tile + st) * TC_KT * 2, row0, xb);
         }
       }
       for (uint32_t i = n > (uint32_t)TC_XSLOTS ? n - TC_XSLOTS : 0; i < n; ++i)
@@ -462,12 +466,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           if constexpr (NMAT == 2) {
             const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
             const float a = args.act == B200MOE_ACT_SILU ? silu_f(gv) : gelu_erf_f(gv);
-            int col = nt * TC_ROWS + row;
+            int col = (nt & 0xffff) * TC_ROWS + row;
             if (args.out_kperm) col = (col & ~7) | ((col & 3) << 1) | ((col >> 2) & 1);
             static_cast<__half*>(args.out)[static_cast<size_t>(tok) * args.N + col] = to_half_sat(a * uv);
           } else {
-            float* o = static_cast<float*>(args.out) + static_cast<size_t>(tok) * args.N +
-                       nt * (2 * TC_ROWS) + row;
+            float* o = static_cast<float*>(args.out) +
+                       static_cast<size_t>(nt >> 16) * args.P * args.N +
+                       static_cast<size_t>(tok) * args.N + (nt & 0xffff) * (2 * TC_ROWS) + row;
             o[0] = __uint_as_float(g[j]);
             o[TC_ROWS] = __uint_as_float(u[j]);
           }
@@ -560,6 +565,7 @@ int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_til
   TcArgs a{};
   a.seg = seg; a.E = gate->experts; a.N = gate->rows; a.K = gate->cols;
   a.ntiles = gate->rows / TC_ROWS; a.tok_tile = tok_tile; a.P = pairs; a.act = act;
+  a.ksplit = 1;
   a.out_kperm = out_kperm;
   a.out = a_out; a.status = device_status_ptr();
   a.total_rows = static_cast<long long>(gate->experts) * gate->rows;
@@ -572,8 +578,30 @@ int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_til
   return tc_launch<B200MOE_LAYOUT_Q8_0, 2>(maps, a, st);
 }
 
+int tc_down_ksplit(const b200moe_weight_t* down, int est_pairs) {
+  // Few tiles (expert-parallel ranks with one or two experts) leave SMs idle:
+  // split the long reduction into up to four partitions when that fills the
+  // waves better.  est_pairs is the expected number of rows, not a bound.
+  const int stages = down->cols / TC_KT;
+  const int sms = sm_count();
+  const int per_expert = est_pairs / (down->experts > 0 ? down->experts : 1);
+  const long long tiles = static_cast<long long>(down->experts) * (down->rows / (2 * TC_ROWS)) *
+                          ((per_expert + 191) / 192 > 0 ? (per_expert + 191) / 192 : 1);
+  if (tiles >= 2ll * sms) return 1;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int ks = 1; ks <= 4; ks *= 2) {
+    if (stages % (4 * ks) != 0) break;
+    const long long items = tiles * ks;
+    const long long waves = (items + sms - 1) / sms;
+    const double eff = static_cast<double>(items) / (waves * sms) - 0.03 * (ks - 1);
+    if (eff > best_eff) { best_eff = eff; best = ks; }
+  }
+  return best;
+}
+
 int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile,
-                   const b200moe_weight_t* down, float* d_out, cudaStream_t st) {
+                   const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st) {
   if (int rc = tc_check(down, "down")) return rc;
   B200_REQUIRE(down->rows % (2 * TC_ROWS) == 0, "tensor kernel: hidden (%d) must be a multiple of 256",
                down->rows);
@@ -585,7 +613,10 @@ int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile
   if (int rc = tc_token_maps(maps, a_in, pairs, static_cast<uint64_t>(down->cols) * 2)) return rc;
   TcArgs a{};
   a.seg = seg; a.E = down->experts; a.N = down->rows; a.K = down->cols;
+  B200_REQUIRE(ksplit >= 1 && (down->cols / TC_KT) % (4 * ksplit) == 0, "tensor kernel: bad k split %d",
+               ksplit);
   a.ntiles = down->rows / (2 * TC_ROWS); a.tok_tile = tok_tile; a.P = pairs; a.act = 0;
+  a.ksplit = ksplit;
   a.out = d_out; a.status = device_status_ptr();
   a.total_rows = static_cast<long long>(down->experts) * down->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;

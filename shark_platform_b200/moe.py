@@ -211,7 +211,7 @@ def grouped_matmul(xs: torch.Tensor, plan_seg: torch.Tensor, w: PreparedWeight, 
     part = torch.empty(ks, max(pairs, 1), w.rows, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         C.check(C.lib.b200moe_down(_ptr(xs), _ptr(plan_seg), pairs, max_segment,
-                                   ctypes.byref(w.desc), regime, _ptr(part), _stream()), "down")
+                                   ctypes.byref(w.desc), regime, ks, _ptr(part), _stream()), "down")
     out = part[0] if ks == 1 else part.sum(dim=0)
     return out[:pairs]
 

@@ -187,7 +187,7 @@ class CudaBackend:
         if ev:
             ev[1].record()
         C.check(C.lib.b200moe_down(self._p(a), self._p(seg), n, max_segment,
-                                   ctypes.byref(L.down.desc), self.regime, self._p(part),
+                                   ctypes.byref(L.down.desc), self.regime, ks, self._p(part),
                                    self._st()), "down")
         if ev:
             ev[2].record()
@@ -267,7 +267,10 @@ class P2PExpertParallelMoeBlock(torch.nn.Module):
         self.ret_y = self.buf[self.off_ret:self.off_ret + self.ret_rows * d * 2].view(torch.bfloat16).view(self.ret_rows, d)
         self.seg2 = torch.zeros(self.el + 1, dtype=torch.int32, device=self.dev)
         self.a = torch.empty(self.cap_rows, layer.ffn, dtype=torch.float16, device=self.dev)
-        self.ks = C.lib.b200moe_down_ksplit(ctypes.byref(layer.down.desc), self.cap_rows,
+        # load balance is steered by the rows expected under uniform routing, the
+        # buffers are sized for the worst case
+        expected = max(1, max_tokens * top_k // self.world)
+        self.ks = C.lib.b200moe_down_ksplit(ctypes.byref(layer.down.desc), expected,
                                             self.max_segment, regime)
         self.dpart = torch.empty(self.ks, self.cap_rows, d, dtype=torch.float32, device=self.dev)
         self.backend = CudaBackend(layer, regime)
@@ -301,7 +304,8 @@ class P2PExpertParallelMoeBlock(torch.nn.Module):
         if ev:
             ev[1].record()
         C.check(C.lib.b200moe_down(p(self.a), p(self.seg2), self.cap_rows, self.max_segment,
-                                   ctypes.byref(L.down.desc), self.regime, p(self.dpart), st), "down")
+                                   ctypes.byref(L.down.desc), self.regime, self.ks, p(self.dpart), st),
+                "down")
         if ev:
             ev[2].record()
             b.timings.append((ev, -1))  # rows received are only known on the device

@@ -343,3 +343,29 @@ def test_stream_kernel_112_row_tiles(M, tokens, skew):
     assert M.device_status() == 0
     assert torch.equal(experts.cpu().to(torch.int64), mid["experts"])
     assert orc.rel_l2(y.cpu() - case.h, want - case.h) < REL_L2_TOL
+
+
+@pytest.mark.parametrize("ksplit", [2, 4])
+def test_tensor_down_ksplit_partials_sum_to_the_unsplit_result(M, ksplit):
+    from shark_platform_b200 import _cabi as C, types as T
+
+    gen = torch.Generator().manual_seed(41)
+    e, n, k, tokens = 2, 256, 2048, 150
+    planes = syn.q8_0_planes(gen, e, n, k)
+    lay = T.BlockScaledLayout([e, n, k], planes["d"].cuda(), planes["qs"].cuda())
+    w = M.prepare_weight(T.PlanarQuantizedTensor(shape=[e, n, k], layout=lay))
+    ex = torch.randint(0, e, (tokens, 1), generator=gen)
+    plan = M.route_plan(ex.cuda(), e)
+    xs = torch.randn(tokens, k, generator=gen).to(torch.float16).cuda()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def run(ks):
+        out = torch.zeros(ks, tokens, n, dtype=torch.float32, device="cuda")
+        C.check(C.lib.b200moe_down(p(xs), p(plan.seg_offsets), tokens, tokens, ctypes.byref(w.desc),
+                                   C.REGIME_TENSOR, ks, p(out), st), "down")
+        return out.sum(dim=0).cpu()
+
+    base, split = run(1), run(ksplit)
+    assert M.device_status() == 0
+    assert orc.rel_l2(split, base) < 1e-5

@@ -41,7 +41,7 @@ def _down_both_ways(seed, tokens, hidden=256, ffn=1024, experts=8, top_k=2):
     ks = C.lib.b200moe_down_ksplit(ctypes.byref(w.desc), pairs, tokens, C.REGIME_STREAM)
     part = torch.zeros(ks, pairs, hidden, dtype=torch.float32, device="cuda")
     C.check(C.lib.b200moe_down(p(a), p(plan.seg_offsets), pairs, tokens, ctypes.byref(w.desc),
-                               C.REGIME_STREAM, p(part), st), "down")
+                               C.REGIME_STREAM, ks, p(part), st), "down")
     want = part[0].clone()
     for c in range(1, ks):
         want += part[c]
