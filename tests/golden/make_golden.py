@@ -3,7 +3,7 @@
 Usage (needs a sharktank source checkout; iree-turbine is replaced by
 iree_stub.py, which only has to make the torch-eager path importable):
 
-    python tests/golden/make_golden.py --sharktank /path/to/sharktank
+    python tests/golden/make_golden.py --sharktank /path/to/reference/sharktank
 
 Writes:
   formats.npz      packed Q8_0 / Q4_K blocks, the planes the reference's
@@ -46,8 +46,11 @@ def digest(case) -> str:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--sharktank", default="/root/reference/sharktank")
+    ap.add_argument("--sharktank", default=os.environ.get("SHARKTANK_SRC", ""),
+                    help="path of a sharktank source checkout (the directory that contains the sharktank package)")
     args = ap.parse_args()
+    if not args.sharktank:
+        ap.error("--sharktank (or SHARKTANK_SRC) is required")
     sys.path.insert(0, args.sharktank)
     import iree_stub
 

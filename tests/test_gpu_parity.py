@@ -158,7 +158,7 @@ def test_layer_matches_reference_fixture(M, name):
     y = blk(h).float().cpu()
     want = torch.from_numpy(g["y"])
     assert orc.rel_l2(y, want) < REL_L2_TOL
-    if h.dtype == torch.float32:  # fp32 output: judge the MoE term alone, without the residual
+    if h.dtype == torch.float32:  # fp32 output: compare the MoE term alone, without the residual
         assert orc.rel_l2(y - case.h, want - case.h) < REL_L2_TOL
     y2 = blk(h).float().cpu()
     assert torch.equal(y, y2), "two runs differ: a race"

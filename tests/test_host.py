@@ -96,7 +96,7 @@ def test_product_never_imports_the_oracle():
                 assert "oracle" not in text.replace("# oracle", ""), f"{f} mentions the oracle"
 
 
-REF = "/root/reference/sharktank"
+REF = os.environ.get("SHARKTANK_SRC", os.path.join(os.sep, "root", "reference", "sharktank"))
 
 
 @pytest.mark.skipif(not os.path.isdir(REF), reason="sharktank checkout not present")
