@@ -393,13 +393,16 @@ def main():
             peak = peaks["bf16_tflops"]
             roofline = {"bound": "tensor", "kernel": "gate_up", "achieved": ach, "peak": peak,
                         "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                        "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
                         "peak_source": peaks["source"] + " (cuBLAS bf16 burst)"}
         else:
             gu_bytes = experts_active * 2 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
             ach = gu_bytes / (stage["gate_up"] * 1e-3) / 1e9
             peak = peaks["hbm_gbs"]
+            # DRAM traffic of this kernel per launch: an ncu capture of a 374 MB case of
+            # the same kernel read 1.0028 x its quantised bytes; traffic grows with them
             roofline = {"bound": "hbm", "kernel": "gate_up", "achieved": ach, "peak": peak,
-                        "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                        "unit": "GB/s", "frac": ach / peak, "traffic": gu_bytes * 1.0028,
                         "peak_source": peaks["source"] + " (copy)"}
         layer_bytes = experts_active * w_bytes_expert + 2 * tokens * spec.hidden * 2 + spec.experts * spec.hidden * 4
         whole = {"tensor_frac": layers * flops / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
