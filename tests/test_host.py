@@ -124,3 +124,66 @@ def test_plugin_registers_ahead_of_sharktank_overrides():
     # CPU tensors: our overrides decline and the reference's own error surfaces
     with pytest.raises(NotImplementedError):
         q[torch.zeros(3, 2, dtype=torch.int64), :, :]
+
+
+def _desc(layout, experts, rows, cols):
+    from shark_platform_b200 import _cabi as C
+
+    return C.WeightDesc(layout, experts, rows, cols, 16, 16, 16)
+
+
+def test_down_ksplit_heuristics_need_no_gpu():
+    """Pure host arithmetic behind b200moe_down_ksplit (148 SMs assumed without a device)."""
+    import ctypes
+
+    from shark_platform_b200 import _cabi as C
+
+    mixtral_down = _desc(C.LAYOUT_Q8_0, 8, 4096, 14336)
+    ks = lambda d, pairs, seg, regime: C.lib.b200moe_down_ksplit(ctypes.byref(d), pairs, seg, regime)
+    assert ks(mixtral_down, 64, 32, C.REGIME_STREAM) == 4      # decode: 1024 items = 6.9 waves
+    assert ks(mixtral_down, 8192, 4096, C.REGIME_STREAM) == 1  # many rows: no partials
+    assert ks(mixtral_down, 8192, 4096, C.REGIME_AUTO) == 1    # prefill, 768 tiles >= 2 waves
+    one_expert = _desc(C.LAYOUT_Q8_0, 1, 4096, 14336)
+    assert ks(one_expert, 1024, 4096, C.REGIME_AUTO) == 4      # one expert per rank: 96 tiles
+    small_k = _desc(C.LAYOUT_Q8_0, 8, 256, 512)
+    assert ks(small_k, 64, 32, C.REGIME_STREAM) == 1           # two stages only
+
+
+def test_kperm_and_workspace_need_no_gpu():
+    import ctypes
+
+    from shark_platform_b200 import _cabi as C
+
+    assert C.lib.b200moe_kperm(C.LAYOUT_Q8_0, C.REGIME_AUTO, 32) == 0
+    assert C.lib.b200moe_kperm(C.LAYOUT_Q4_K, C.REGIME_AUTO, 32) == 1
+    assert C.lib.b200moe_kperm(C.LAYOUT_Q4_K, C.REGIME_TENSOR, 4096) == 1
+    layer = C.LayerDesc()
+    layer.hidden, layer.ffn, layer.experts, layer.top_k = 4096, 14336, 8, 2
+    layer.gate = _desc(C.LAYOUT_Q8_0, 8, 14336, 4096)
+    layer.up = _desc(C.LAYOUT_Q8_0, 8, 14336, 4096)
+    layer.down = _desc(C.LAYOUT_Q8_0, 8, 4096, 14336)
+    small = C.lib.b200moe_workspace_bytes(ctypes.byref(layer), 32)
+    big = C.lib.b200moe_workspace_bytes(ctypes.byref(layer), 4096)
+    # xs + A + D dominate: pairs * (d*2 + F*2 + ksplit*d*4) bytes
+    assert 64 * (4096 * 2 + 14336 * 2 + 4 * 4096 * 4) <= small < 16 * 2**20
+    assert 8192 * (4096 * 2 + 14336 * 2 + 4096 * 4) <= big < 600 * 2**20
+    assert C.lib.b200moe_workspace_bytes(None, 32) == 0
+
+
+def test_entry_points_reject_bad_arguments_without_touching_the_gpu():
+    import ctypes
+
+    from shark_platform_b200 import _cabi as C
+
+    dummy = ctypes.c_void_p(256)
+    bad = _desc(7, 8, 256, 512)  # unknown layout
+    rc = C.lib.b200moe_dequant(ctypes.byref(bad), C.DT_F16, dummy, None)
+    assert rc == -1 and "unknown layout" in C.last_error()
+    rc = C.lib.b200moe_gate_up(dummy, dummy, 8, 8, None, None, 0, 0, 0, dummy, None)
+    assert rc == -1 and "NULL" in C.last_error()
+    ep = C.EpDesc()
+    ep.world, ep.rank, ep.experts_local = 40, 0, 1
+    rc = C.lib.b200moe_ep_barrier(ctypes.byref(ep), 1, None, None)
+    assert rc == -1 and "out of range" in C.last_error()
+    with pytest.raises(C.B200MoeError):
+        C.check(rc, "ep_barrier")
