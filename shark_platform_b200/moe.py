@@ -430,6 +430,54 @@ def einsum_2args_gate_scale(input0, input1, einsum_str):
     return a.unsqueeze(-1) * b
 
 
+def matmul_quantized(lhs, rhs, *, transpose_rhs: bool = False):
+    """`matmul(x, W, transpose_rhs=True)` with a Q8_0 / Q4_K planar weight
+    [N, K]: the dense quantized linear of the same models (attention
+    projections, output head), run as the grouped product with one expert.
+    Replaces the IREE kernel routing of ops/custom_impls.py:66-128 and the
+    dequantise-then-matmul default (ops/default_impls.py:345-359)."""
+    if not transpose_rhs or _layout_name(rhs) not in _SUPPORTED:
+        return NotImplemented
+    x = _unbox(lhs)
+    if not x.is_cuda or len(rhs.shape) != 2:
+        return NotImplemented
+    n, k = (int(v) for v in rhs.shape)
+    if k % 256 != 0 or n % 256 != 0 or x.shape[-1] != k:
+        return NotImplemented
+
+    class _AsExperts:  # the same planes seen as a stack of one expert
+        pass
+
+    holder = getattr(rhs, "_b200moe_as_experts", None)
+    if holder is None:
+        holder = _AsExperts()
+        holder.layout_type = rhs.layout_type
+        holder.shape = [1, n, k]
+        holder.unpack = rhs.unpack
+        try:
+            rhs._b200moe_as_experts = holder
+        except AttributeError:
+            pass
+    w = prepare_weight(holder)
+    rows = x.reshape(-1, k).to(torch.float16).contiguous()
+    m = rows.shape[0]
+    if C.lib.b200moe_kperm(w.layout, C.REGIME_AUTO, m):
+        rows = rows.view(m, -1, 2, 4).transpose(2, 3).reshape(m, -1).contiguous()
+    seg = torch.tensor([0, m], dtype=torch.int32, device=x.device)
+    out = grouped_matmul(rows, seg, w, max(m, 1))
+    return out.view(*x.shape[:-1], n).to(x.dtype)
+
+
+def linear_quantized(input, weight, bias=None, *, accum_dtype=None):
+    """`linear(x, W, bias)` for the same weights (ops/qlinear_impls.py:158-172)."""
+    y = matmul_quantized(input, weight, transpose_rhs=True)
+    if y is NotImplemented:
+        return NotImplemented
+    if bias is not None:
+        y = y + _unbox(bias).to(y.dtype)
+    return y
+
+
 def register_overrides(ops_module=_ops, quantized_type=None, tensor_type=torch.Tensor, salience=10):
     """Registers the overrides with an ops registry: this package's mirror by
     default, sharktank's own when called from `plugin.register`."""
@@ -439,8 +487,14 @@ def register_overrides(ops_module=_ops, quantized_type=None, tensor_type=torch.T
     ops_module.get_index.override(qt, salience=salience)(get_index_quantized)
     ops_module.einsum_2args.override(tensor_type, GatheredExperts, salience=salience)(
         einsum_2args_gathered)
+    ops_module.matmul.override(tensor_type, qt, salience=salience)(matmul_quantized)
     if ops_module is _ops:
+        ops_module.linear.override(tensor_type, qt, salience=salience)(linear_quantized)
         ops_module.einsum_2args.override(torch.Tensor, torch.Tensor)(einsum_2args_gate_scale)
+    else:
+        # sharktank dispatches linear on (input, weight) and (input, weight, bias)
+        ops_module.linear.override(tensor_type, qt, salience=salience)(linear_quantized)
+        ops_module.linear.override(tensor_type, qt, tensor_type, salience=salience)(linear_quantized)
 
 
 register_overrides()

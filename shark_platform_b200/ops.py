@@ -106,3 +106,16 @@ def elementwise(operator, *args, **kwargs):
 def _elementwise_tensor(operator, x, *args, **kwargs):
     # ops/default_impls.py:125-128
     return operator(x, *args, **kwargs)
+
+
+@overridable(0, 1)
+def matmul(lhs, rhs, *, transpose_rhs: bool = False):
+    """Performs a matmul where the RHS may be an InferenceTensor
+    (sharktank/ops/signatures.py:659-688)."""
+
+
+@overridable(0, 1)
+def linear(input, weight, bias=None, *, accum_dtype=None):
+    """Applies a linear transformation `input @ weight.T + bias`
+    (sharktank/ops/signatures.py:615-656).  The reference dispatches on
+    (input, weight[, bias]); the mirror dispatches on (input, weight)."""

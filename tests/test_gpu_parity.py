@@ -369,3 +369,34 @@ def test_tensor_down_ksplit_partials_sum_to_the_unsplit_result(M, ksplit):
     base, split = run(1), run(ksplit)
     assert M.device_status() == 0
     assert orc.rel_l2(split, base) < 1e-5
+
+
+@pytest.mark.parametrize("kind", [syn.Q8_0, syn.Q4_K])
+@pytest.mark.parametrize("rows", [1, 5, 40, 300])
+def test_quantized_dense_linear_through_the_registry(M, kind, rows):
+    """ops.linear / ops.matmul on a Q8_0 / Q4_K [N, K] weight (attention
+    projections, output head) = the grouped product with one expert."""
+    from shark_platform_b200 import ops, types as T
+
+    n, k = 512, 768
+    gen = torch.Generator().manual_seed(900 + rows)
+    mk = syn.q8_0_planes if kind == syn.Q8_0 else syn.q4_k_planes
+    planes = {name: v[0] for name, v in mk(gen, 1, n, k).items()}
+    dense = torch.from_numpy(orc.dequant(kind, np_planes(planes))).float()
+    cuda = {name: v.cuda() for name, v in planes.items()}
+    lay = (T.BlockScaledLayout([n, k], cuda["d"], cuda["qs"]) if kind == syn.Q8_0
+           else T.SuperBlockOffsetScaled_4_6_Layout([n, k], **cuda))
+    w = T.PlanarQuantizedTensor(shape=[n, k], layout=lay)
+    x = torch.randn(2, rows, k, generator=gen)
+    bias = torch.randn(n, generator=gen)
+    want = x @ dense.mT + bias
+    ops._test_enable_last_op_dispatch(True)
+    got = ops.linear(x.cuda(), w, T.DefaultPrimitiveTensor(data=bias.cuda()))
+    assert ops._test_get_last_op_dispatch() is M.linear_quantized
+    got2 = ops.matmul(x.cuda(), w, transpose_rhs=True)
+    assert ops._test_get_last_op_dispatch() is M.matmul_quantized
+    ops._test_enable_last_op_dispatch(False)
+    assert M.device_status() == 0
+    assert got.shape == (2, rows, n)
+    assert orc.rel_l2(got.cpu(), want) < 5e-3
+    assert orc.rel_l2(got2.cpu(), want - bias) < 5e-3

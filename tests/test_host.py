@@ -124,6 +124,16 @@ def test_plugin_registers_ahead_of_sharktank_overrides():
     # CPU tensors: our overrides decline and the reference's own error surfaces
     with pytest.raises(NotImplementedError):
         q[torch.zeros(3, 2, dtype=torch.int64), :, :]
+    # dense quantized linear / matmul: consulted first, declined on the CPU, after
+    # which dispatch goes on to the reference's own IREE kernel (stubbed out here)
+    lay2 = BlockScaledLayout([256, 256], torch.ones(256, 8, 1, dtype=torch.float16),
+                             torch.ones(256, 8, 32, dtype=torch.int8))
+    q2 = PlanarQuantizedTensor(shape=[256, 256], layout=lay2)
+    x = torch.ones(3, 256)
+    assert next(iter(st_ops.matmul.find_overrides((x, q2)))) is moe.matmul_quantized
+    assert next(iter(st_ops.linear.find_overrides((x, q2)))) is moe.linear_quantized
+    with pytest.raises(RuntimeError, match="mmt_block_scaled_q8 unavailable"):
+        st_ops.linear(x, q2)
 
 
 def _desc(layout, experts, rows, cols):
