@@ -173,8 +173,9 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
  * array built into the library (held by every GPU that loads it until the
  * process exits) and the caller receives the finished sums.
  * d_out: fp32 [pairs, d]; rows at and after seg_offsets[experts] are set to 0.
- * Limit: ksplit * pairs * d <= 2,097,152 floats with ksplit =
- * b200moe_down_ksplit(...) (e.g. 128 pairs at d = 4096); larger calls fail with
+ * Always runs the weight-streaming kernel.  Limit: ksplit * pairs * d <=
+ * 2,097,152 floats with ksplit = b200moe_down_ksplit(down, pairs, max_segment,
+ * B200MOE_REGIME_STREAM) (e.g. 128 pairs at d = 4096); larger calls fail with
  * B200MOE_ERR_INVALID and a message.  Calls no cudaMalloc / cudaFree.
  * The first call on each device looks up the array's device address
  * (cudaGetSymbolAddress): make that first call outside any stream capture.
