@@ -65,6 +65,11 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+// Orders this thread's generic-proxy shared-memory accesses (ld.shared /
+// st.shared) against async-proxy accesses (TMA).  A buffer that TMA refills
+// needs it on the release path as well: ld.shared reads followed by a TMA
+// write of the same bytes are a cross-proxy write-after-read, which the
+// mbarrier release/acquire pair alone does not order.
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -90,10 +95,12 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait.  Gives up after ~2^31 clock ticks (about a second), records
 // DEV_ERR_WAIT_TIMEOUT in the status word and raises the CTA-wide abort flag so
 // that every later wait in this CTA returns at once.  Returns false on abort.
+// The barrier is tried first: a phase that has already completed costs one
+// try_wait and no shared-memory load of the abort flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int32_t* status) {
-  if (*abort_flag) return false;
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;

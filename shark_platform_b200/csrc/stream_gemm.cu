@@ -171,6 +171,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
           const int slot = n % STAGES;
           const uint32_t phase = (n / STAGES) & 1u;
           if (!mbar_wait(empty_bar(slot), phase ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          fence_proxy_async_smem();
           const uint32_t sb = smem_base + slot * C::STAGE;
           const uint32_t fb = full_bar(slot);
           mbar_expect_tx(fb, tx_bytes);
@@ -365,6 +366,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
           }
         }
       }
+      fence_proxy_async_smem();  // reads done before TMA may refill the stage
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(slot));
     }

@@ -279,6 +279,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             const uint32_t g = n / TC_SGROUP;
             const int ss = g % TC_SSLOTS;
             if (!mbar_wait(sempty + 8u * ss, ((g / TC_SSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+            fence_proxy_async_smem();
             const uint32_t sdst = scale_base + ss * TC_SSLOT;
             const uint32_t sb = sfull + 8u * ss;
             mbar_expect_tx(sb, 2 * SSET_BYTES);
@@ -297,6 +298,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           const uint32_t wi = n >> 1;
           const int ws = wi % TC_WSLOTS;
           if (!mbar_wait(wempty + 8u * ws, ((wi / TC_WSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          fence_proxy_async_smem();
           const uint32_t wdst = smem_base + ws * TC_WSLOT;
           const uint32_t wb = wfull + 8u * ws;
           mbar_expect_tx(wb, 2 * WSET_BYTES);
@@ -397,6 +399,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         } else {
           lds128(scale_base + ss * TC_SSLOT + set * TC_SSET + row * 16, *reinterpret_cast<uint32_t(*)[4]>(&scw[0]));
         }
+        fence_proxy_async_smem();  // reads done before TMA may refill the slot
         __syncwarp();
         if (lane == 0) mbar_arrive(sempty + 8u * ss);
 #pragma unroll
@@ -415,6 +418,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             uint32_t q[2][4];
 #pragma unroll
             for (int c = 0; c < 2; ++c) lds128(wrow + (((2 * grp + c) ^ sw64) << 4), q[c]);
+            fence_proxy_async_smem();  // reads done before TMA may refill the slot
             __syncwarp();
             if (lane == 0) mbar_arrive(wempty + 8u * ws);
 #pragma unroll
@@ -431,6 +435,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             uint32_t q[4][4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) lds128(wrow + (((4 * grp + c) ^ sw) << 4), q[c]);
+            fence_proxy_async_smem();  // reads done before TMA may refill the slot
             __syncwarp();
             if (lane == 0) mbar_arrive(wempty + 8u * ws);
             const __half2 s_lo = u32_as_h2(__byte_perm(scw[s4], scw[s4], 0x1010));
