@@ -240,12 +240,63 @@ def unbox_tensor(t: Union[torch.Tensor, InferenceTensor]) -> torch.Tensor:
     raise TypeError(f"cannot unbox {type(t).__name__}")
 
 
+def _nest(flat: dict) -> dict:
+    """Splits dotted keys into nested dicts and merges them with dicts already
+    present ({"a.b": 0, "a": {"c": 1}} -> {"a": {"b": 0, "c": 1}}), as
+    types/theta.py:227-270 does.  A tree without dotted keys comes back as is."""
+    if not any(isinstance(k, str) and "." in k for k in flat) and not any(
+        isinstance(v, dict) for v in flat.values()
+    ):
+        return flat
+    nested: dict = {}
+
+    def add(dst: dict, key, value):
+        parts = str(key).split(".")
+        for part in parts[:-1]:
+            nxt = dst.setdefault(part, {})
+            if not isinstance(nxt, dict):
+                raise ValueError(f"Name conflict at '{part}' while nesting '{key}'")
+            dst = nxt
+        leaf = parts[-1]
+        if isinstance(value, dict):
+            sub = dst.setdefault(leaf, {})
+            if not isinstance(sub, dict):
+                raise ValueError(f"Name conflict at '{leaf}' while nesting '{key}'")
+            for k2, v2 in value.items():
+                add(sub, k2, v2)
+        else:
+            if isinstance(dst.get(leaf), dict):
+                raise ValueError(f"Name conflict at '{leaf}' while nesting '{key}'")
+            dst[leaf] = value
+
+    for k, v in flat.items():
+        add(nested, k, v)
+    return nested
+
+
 class Theta:
     """types/theta.py:71-214: nested dict of inference tensors addressed by
     dotted names."""
 
-    def __init__(self, tree: dict):
-        self._tree = tree
+    def __init__(self, tree):
+        if not isinstance(tree, dict):
+            tree = {t.name: t for t in tree}
+        self._tree = _nest(tree)
+
+    def flatten(self) -> dict:
+        """Leaf tensors keyed by their dotted path (types/theta.py:121-134)."""
+        out = {}
+
+        def walk(prefix, node):
+            for key, value in node.items():
+                path = f"{prefix}.{key}" if prefix else str(key)
+                if isinstance(value, dict):
+                    walk(path, value)
+                else:
+                    out[path] = value
+
+        walk("", self._tree)
+        return out
 
     @property
     def keys(self):
