@@ -223,12 +223,15 @@ def main():
         stack = B200MoeStack(blocks)
         h = device_input(case, dev).reshape(tokens, spec.hidden).contiguous()
         step = lambda: stack(h)
-        launches_per_step = 6 * layers
+        fused = C.lib.b200moe_front_supported(tokens, ctypes.byref(block.layer.desc))
+        launches_per_step = (4 if fused else 6) * layers
     elif world == 1:
         block = b200_block(case, regime=args.regime, device=dev)
         h = device_input(case, dev).reshape(tokens, spec.hidden).contiguous()
         step = lambda: block(h)
-        launches_per_step = 6
+        # router, plan and permutation are one launch for small token counts
+        fused = C.lib.b200moe_front_supported(tokens, ctypes.byref(block.layer.desc))
+        launches_per_step = 4 if fused else 6
     else:
         from shark_platform_b200 import parallel
 

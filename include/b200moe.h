@@ -129,6 +129,19 @@ int b200moe_route_plan(const int32_t* experts, int32_t pairs, int32_t expert_beg
                        int32_t experts_local, int32_t* counts, int32_t* seg_offsets,
                        int32_t* perm, int32_t* inv, void* stream);
 
+/* Decode front end in one launch: b200moe_router + b200moe_route_plan (all
+ * experts local, expert_begin 0) + b200moe_permute_rows, with bit-identical
+ * outputs except that the fp16 copy of the normalised rows is not produced.
+ * One CTA per token in a cooperative launch; b200moe_front_supported says
+ * whether the shape qualifies (at most 128 tokens, hidden <= 8192 and a
+ * multiple of 256).  No reference counterpart: the reference runs these steps
+ * as separate torch operators (layers/mixture_of_experts_block.py:66-83,
+ * layers/ffn_moe_block.py:37-41). */
+int b200moe_front_supported(int32_t tokens, const b200moe_layer_t* layer);
+int b200moe_front(const void* h, int h_dtype, int32_t tokens, const b200moe_layer_t* layer,
+                  int kperm, int32_t* experts_out, float* gates_out, int32_t* counts,
+                  int32_t* seg_offsets, int32_t* perm, int32_t* inv, void* xs_out, void* stream);
+
 /* xs[pos,:] = xn[perm[pos] / top_k,:] for pos < seg_offsets[E_local]: the rows
  * each expert multiplies, contiguous per expert (replaces the per-token weight
  * gather `weights[experts]` of layers/ffn_moe_block.py:37-41). */

@@ -97,6 +97,8 @@ _PROTOS = {
     "b200moe_gguf_unpack_q8_0": (c_int, [_P, c_int64, _P, _P, _P]),
     "b200moe_gguf_unpack_q4_k": (c_int, [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b200moe_router": (c_int, [_P, c_int, c_int32, _L, _P, _P, _P, _P]),
+    "b200moe_front_supported": (c_int, [c_int32, _L]),
+    "b200moe_front": (c_int, [_P, c_int, c_int32, _L, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b200moe_route_plan": (c_int, [_P, c_int32, c_int32, c_int32, _P, _P, _P, _P, _P]),
     "b200moe_permute_rows": (c_int, [_P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32, _P, _P]),
     "b200moe_kperm": (c_int, [c_int, c_int, c_int32]),

@@ -227,10 +227,29 @@ int b200moe_device_status(void* stream, int32_t* status_out) {
   B200_CHECK_CUDA(cudaStreamSynchronize(st));
   if (status_out) *status_out = v;
   if (v != 0) {
+    clear_front_sync(st);  // a timed-out grid barrier leaves its counters behind
+    cudaStreamSynchronize(st);
     set_error("device status word = %d (1: bounded wait timed out, 2: bounds check, 4: tmem)", v);
     return B200MOE_ERR_DEVICE;
   }
   return B200MOE_OK;
+}
+
+int b200moe_front_supported(int32_t tokens, const b200moe_layer_t* layer) {
+  return layer != nullptr && front_fused_supported(tokens, layer) ? 1 : 0;
+}
+
+int b200moe_front(const void* h, int h_dtype, int32_t tokens, const b200moe_layer_t* layer,
+                  int kperm, int32_t* experts_out, float* gates_out, int32_t* counts,
+                  int32_t* seg_offsets, int32_t* perm, int32_t* inv, void* xs_out, void* stream) {
+  B200_REQUIRE(layer, "front: NULL layer");
+  B200_REQUIRE(layer->ffn_norm_weight && layer->router_weight, "front: NULL router parameters");
+  B200_REQUIRE(h && experts_out && gates_out && counts && seg_offsets && perm && inv && xs_out,
+               "front: NULL buffer");
+  int32_t* status = device_status_ptr();
+  if (status == nullptr) return B200MOE_ERR_CUDA;
+  return launch_front_fused(h, h_dtype, tokens, layer, experts_out, gates_out, counts, seg_offsets,
+                            perm, inv, kperm != 0, xs_out, status, static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_dequant(const b200moe_weight_t* w, int out_dtype, void* out, void* stream) {
@@ -390,16 +409,27 @@ int b200moe_layer_forward(const b200moe_layer_t* L, const void* h, void* y, int 
   const int pairs = tokens * L->top_k;
   const int E = L->experts;
   const int pc = (g_prof.on && g_prof.used < PROF_CALLS) ? g_prof.used++ : -1;
-  prof_mark(pc, 0, st);
-  if (int rc = launch_router(h, io_dtype, tokens, L, w.xn, w.experts, w.gates, st)) return rc;
-  prof_mark(pc, 1, st);
-  if (int rc = launch_route_plan(w.experts, pairs, 0, E, w.counts, w.seg, w.perm, w.inv, st))
-    return rc;
-  prof_mark(pc, 2, st);
   const int kp_in = b200moe_kperm(L->gate.layout, regime, tokens);
   const int kp_mid = b200moe_kperm(L->down.layout, regime, tokens);
-  if (int rc = launch_permute_rows(w.xn, w.perm, w.seg, E, pairs, L->top_k, L->hidden, kp_in, w.xs, st))
-    return rc;
+  prof_mark(pc, 0, st);
+  if (front_fused_supported(tokens, L)) {
+    // decode: one launch; its time is booked under the router stage
+    int32_t* status = device_status_ptr();
+    if (status == nullptr) return B200MOE_ERR_CUDA;
+    if (int rc = launch_front_fused(h, io_dtype, tokens, L, w.experts, w.gates, w.counts, w.seg,
+                                    w.perm, w.inv, kp_in, w.xs, status, st))
+      return rc;
+    prof_mark(pc, 1, st);
+    prof_mark(pc, 2, st);
+  } else {
+    if (int rc = launch_router(h, io_dtype, tokens, L, w.xn, w.experts, w.gates, st)) return rc;
+    prof_mark(pc, 1, st);
+    if (int rc = launch_route_plan(w.experts, pairs, 0, E, w.counts, w.seg, w.perm, w.inv, st))
+      return rc;
+    prof_mark(pc, 2, st);
+    if (int rc = launch_permute_rows(w.xn, w.perm, w.seg, E, pairs, L->top_k, L->hidden, kp_in, w.xs, st))
+      return rc;
+  }
   prof_mark(pc, 3, st);
   if (int rc = b200moe_gate_up(w.xs, w.seg, pairs, tokens, &L->gate, &L->up, L->activation, regime,
                                kp_mid, w.a, stream))

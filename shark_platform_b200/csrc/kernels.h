@@ -10,6 +10,13 @@ int launch_route_plan(const int32_t* experts, int pairs, int e_begin, int E, int
                       int32_t* seg, int32_t* perm, int32_t* inv, cudaStream_t st);
 int launch_permute_rows(const void* xn, const int32_t* perm, const int32_t* seg, int E, int pairs,
                         int k, int d, int kperm, void* xs, cudaStream_t st);
+// router + route plan + permutation in one cooperative launch (small token counts)
+bool front_fused_supported(int tokens, const b200moe_layer_t* L);
+int launch_front_fused(const void* h, int h_dtype, int tokens, const b200moe_layer_t* L,
+                       int32_t* experts, float* gates, int32_t* counts, int32_t* seg,
+                       int32_t* perm, int32_t* inv, int kperm, void* xs, int32_t* status,
+                       cudaStream_t st);
+int clear_front_sync(cudaStream_t st);
 int launch_exchange_plan(const int32_t* counts, int world, int el, int32_t* seg, int32_t* perm,
                          int32_t* inv, cudaStream_t st);
 int launch_gather_rows(const void* rows, const int32_t* idx, int n, int div, int row_bytes,

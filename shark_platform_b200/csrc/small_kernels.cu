@@ -1,7 +1,10 @@
 // Router, route plan, row permutation, combine, reference dequantisation and
 // GGUF block unpacking.  All HBM-bound or latency-bound helpers around the two
 // expert-GEMM kernels.
+#include <atomic>
+
 #include "common.cuh"
+#include "kernels.h"
 
 namespace b200moe {
 
@@ -199,19 +202,23 @@ __device__ __forceinline__ void router_select(const float* logit, int lane, int 
 constexpr int RB_THREADS = 256;
 constexpr int RB_MAXV = 4;  // 8-element vectors per thread
 
+// Router for the token of this CTA.  Leaves the normalised row in `x` (this
+// thread's 8-element vectors tid + v*RB_THREADS); writes it as fp16 to xn_row
+// unless that is null; warp 0 writes the token's experts and gates.
 template <typename T>
-__global__ void __launch_bounds__(RB_THREADS)
-router_block_kernel(const T* __restrict__ h, int d, int E, int k, float eps,
-                    const float* __restrict__ norm_w, const float* __restrict__ rw,
-                    const float* __restrict__ rb, __half* __restrict__ xn_out,
-                    int32_t* __restrict__ experts_out, float* __restrict__ gates_out) {
+__device__ __forceinline__ void router_block_body(const T* __restrict__ row, int d, int E, int k,
+                                                  float eps, const float* __restrict__ norm_w,
+                                                  const float* __restrict__ rw,
+                                                  const float* __restrict__ rb,
+                                                  __half* __restrict__ xn_row,
+                                                  int32_t* __restrict__ experts_row,
+                                                  float* __restrict__ gates_row,
+                                                  float (&x)[RB_MAXV][8]) {
   __shared__ float s_part[RB_THREADS / 32][8];
   __shared__ float s_logit[MAX_EXPERTS];
   __shared__ float s_ss[RB_THREADS / 32];
-  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const T* row = h + static_cast<size_t>(t) * d;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nvec = d / 8;
-  float x[RB_MAXV][8];
   float ss = 0.f;
 #pragma unroll
   for (int v = 0; v < RB_MAXV; ++v) {
@@ -236,14 +243,15 @@ router_block_kernel(const T* __restrict__ h, int d, int E, int k, float eps,
     if (j < nvec) {
       float w[8];
       load8<float>(norm_w + j * 8, w);
-      uint32_t packed[4];
 #pragma unroll
       for (int i = 0; i < 8; ++i) x[v][i] = w[i] * (x[v][i] * rstd);
+      if (xn_row != nullptr) {
+        uint32_t packed[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        packed[i] = h2_as_u32(__halves2half2(to_half_sat(x[v][2 * i]), to_half_sat(x[v][2 * i + 1])));
-      *reinterpret_cast<uint4*>(xn_out + static_cast<size_t>(t) * d + j * 8) =
-          make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        for (int i = 0; i < 4; ++i)
+          packed[i] = h2_as_u32(__halves2half2(to_half_sat(x[v][2 * i]), to_half_sat(x[v][2 * i + 1])));
+        *reinterpret_cast<uint4*>(xn_row + j * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
     }
   }
   for (int e0 = 0; e0 < E; e0 += 8) {
@@ -280,9 +288,225 @@ router_block_kernel(const T* __restrict__ h, int d, int E, int k, float eps,
     }
     __syncthreads();
   }
-  if (warp == 0)
-    router_select(s_logit, lane, E, k, experts_out + static_cast<size_t>(t) * k,
-                  gates_out + static_cast<size_t>(t) * k);
+  if (warp == 0) router_select(s_logit, lane, E, k, experts_row, gates_row);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RB_THREADS)
+router_block_kernel(const T* __restrict__ h, int d, int E, int k, float eps,
+                    const float* __restrict__ norm_w, const float* __restrict__ rw,
+                    const float* __restrict__ rb, __half* __restrict__ xn_out,
+                    int32_t* __restrict__ experts_out, float* __restrict__ gates_out) {
+  const size_t t = blockIdx.x;
+  float x[RB_MAXV][8];
+  router_block_body<T>(h + t * d, d, E, k, eps, norm_w, rw, rb, xn_out + t * d,
+                       experts_out + t * k, gates_out + t * k, x);
+}
+
+// ------------------------------------------------- fused decode front end
+// Router, route plan and row permutation in one cooperative launch, one CTA
+// per token (tokens <= FRONT_MAX_TOKENS).  After its token's experts are known
+// every CTA meets the others at a grid-wide barrier, ranks its own k pairs
+// among all pairs (stable by pair index, as route_plan_kernel does) and stores
+// the normalised row, still in registers, at its k sorted positions.  Outputs
+// are bit-identical to router_block_kernel + route_plan_kernel +
+// permute_rows_kernel; the fp16 copy of the normalised rows is not written.
+constexpr int FRONT_MAX_TOKENS = 128;
+constexpr int FRONT_MAX_PAIRS = FRONT_MAX_TOKENS * MAX_TOPK;
+constexpr int FRONT_PAIRS_PER_THREAD = FRONT_MAX_PAIRS / RB_THREADS;
+constexpr int FRONT_SYNC_SLOTS = 32;
+
+// {arrived, departed} per slot; zero between launches (the last CTA to leave
+// the barrier resets its slot).  The host hands slots out round-robin, so up to
+// FRONT_SYNC_SLOTS launches may be in flight on one device.
+__device__ unsigned g_front_sync[FRONT_SYNC_SLOTS][2];
+
+// Bounded grid-wide meeting point for a cooperative launch of `n` CTAs.
+// Returns false if the others did not arrive within ~2^31 clock ticks (the
+// status word then carries DEV_ERR_WAIT_TIMEOUT and the slot is left for the
+// host to clear).
+__device__ __forceinline__ bool front_grid_meet(unsigned* sync, unsigned n, int32_t* status) {
+  __shared__ int s_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(&sync[0], 1u);
+    const long long t0 = clock64();
+    int ok = 1;
+    while (*reinterpret_cast<volatile unsigned*>(&sync[0]) < n) {
+      if (clock64() - t0 > (1ll << 31)) {
+        atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
+        ok = 0;
+        break;
+      }
+    }
+    __threadfence();
+    if (ok && atomicAdd(&sync[1], 1u) == n - 1) {
+      // everyone has seen arrived == n: nobody reads the slot again
+      *reinterpret_cast<volatile unsigned*>(&sync[0]) = 0;
+      *reinterpret_cast<volatile unsigned*>(&sync[1]) = 0;
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RB_THREADS)
+front_fused_kernel(const T* __restrict__ h, int d, int E, int k, float eps,
+                   const float* __restrict__ norm_w, const float* __restrict__ rw,
+                   const float* __restrict__ rb, int32_t* experts_out, float* __restrict__ gates_out,
+                   int32_t* __restrict__ counts, int32_t* __restrict__ seg,
+                   int32_t* __restrict__ perm, int32_t* __restrict__ inv, int kperm,
+                   uint4* __restrict__ xs, unsigned* sync, int32_t* status) {
+  __shared__ int s_total[MAX_EXPERTS];
+  __shared__ int s_seg[MAX_EXPERTS + 1];
+  __shared__ int s_rank[MAX_TOPK];
+  const int tid = threadIdx.x;
+  const int t = blockIdx.x, tokens = gridDim.x, pairs = tokens * k;
+  float x[RB_MAXV][8];
+  router_block_body<T>(h + static_cast<size_t>(t) * d, d, E, k, eps, norm_w, rw, rb, nullptr,
+                       experts_out + static_cast<size_t>(t) * k, gates_out + static_cast<size_t>(t) * k, x);
+  if (tid < MAX_EXPERTS) s_total[tid] = 0;
+  if (tid < MAX_TOPK) s_rank[tid] = 0;
+  if (!front_grid_meet(sync, static_cast<unsigned>(tokens), status)) return;
+
+  // every CTA sees all pairs; mine are p0 .. p0+k-1
+  const int p0 = t * k;
+  int mine[MAX_TOPK];
+#pragma unroll
+  for (int i = 0; i < MAX_TOPK; ++i) mine[i] = i < k ? __ldcg(experts_out + p0 + i) : -1;
+  int before[MAX_TOPK];
+#pragma unroll
+  for (int i = 0; i < MAX_TOPK; ++i) before[i] = 0;
+#pragma unroll
+  for (int r = 0; r < FRONT_PAIRS_PER_THREAD; ++r) {
+    const int q = tid + r * RB_THREADS;
+    if (q < pairs) {
+      const int e = __ldcg(experts_out + q);
+      if (e >= 0 && e < E) atomicAdd(&s_total[e], 1);
+#pragma unroll
+      for (int i = 0; i < MAX_TOPK; ++i)
+        if (i < k && q < p0 + i && e == mine[i]) ++before[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAX_TOPK; ++i) {
+    if (i < k) {
+      int c = before[i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+      if ((tid & 31) == 0 && c != 0) atomicAdd(&s_rank[i], c);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      s_seg[e] = run;
+      run += s_total[e];
+    }
+    s_seg[E] = run;
+  }
+  __syncthreads();
+  if (t == 0 && tid <= E) {
+    seg[tid] = s_seg[tid];
+    if (tid < E) counts[tid] = s_total[tid];
+  }
+  int pos[MAX_TOPK];
+#pragma unroll
+  for (int i = 0; i < MAX_TOPK; ++i) {
+    pos[i] = i < k ? s_seg[mine[i]] + s_rank[i] : 0;
+    if (i < k && tid == i) {
+      perm[pos[i]] = p0 + i;
+      inv[p0 + i] = pos[i];
+    }
+  }
+  // the row goes from registers to its k sorted positions
+  const int nvec = d / 8;
+#pragma unroll
+  for (int v = 0; v < RB_MAXV; ++v) {
+    const int j = tid + v * RB_THREADS;
+    if (j < nvec) {
+      uint4 o;
+      if (kperm) {  // halves in the order 0,4,1,5,2,6,3,7 (see permute_rows_kernel)
+        o.x = h2_as_u32(__halves2half2(to_half_sat(x[v][0]), to_half_sat(x[v][4])));
+        o.y = h2_as_u32(__halves2half2(to_half_sat(x[v][1]), to_half_sat(x[v][5])));
+        o.z = h2_as_u32(__halves2half2(to_half_sat(x[v][2]), to_half_sat(x[v][6])));
+        o.w = h2_as_u32(__halves2half2(to_half_sat(x[v][3]), to_half_sat(x[v][7])));
+      } else {
+        o.x = h2_as_u32(__halves2half2(to_half_sat(x[v][0]), to_half_sat(x[v][1])));
+        o.y = h2_as_u32(__halves2half2(to_half_sat(x[v][2]), to_half_sat(x[v][3])));
+        o.z = h2_as_u32(__halves2half2(to_half_sat(x[v][4]), to_half_sat(x[v][5])));
+        o.w = h2_as_u32(__halves2half2(to_half_sat(x[v][6]), to_half_sat(x[v][7])));
+      }
+#pragma unroll
+      for (int i = 0; i < MAX_TOPK; ++i) {
+        if (i < k) xs[static_cast<size_t>(pos[i]) * nvec + j] = o;
+      }
+    }
+  }
+}
+
+// Address of g_front_sync on the current device (cached per device).
+static unsigned* front_sync_base() {
+  static unsigned* ptrs[16] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) {
+    set_error("front: no usable current device");
+    return nullptr;
+  }
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_front_sync);
+    if (e != cudaSuccess) {
+      cuda_fail(e, "cudaGetSymbolAddress(g_front_sync)");
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<unsigned*>(p);
+  }
+  return ptrs[dev];
+}
+
+bool front_fused_supported(int tokens, const b200moe_layer_t* L) {
+  return tokens >= 1 && tokens <= FRONT_MAX_TOKENS && L->hidden <= 8 * RB_THREADS * RB_MAXV &&
+         L->hidden % 256 == 0 && L->top_k >= 1 && L->top_k <= MAX_TOPK && L->experts <= MAX_EXPERTS;
+}
+
+int launch_front_fused(const void* h, int h_dtype, int tokens, const b200moe_layer_t* L,
+                       int32_t* experts, float* gates, int32_t* counts, int32_t* seg,
+                       int32_t* perm, int32_t* inv, int kperm, void* xs, int32_t* status,
+                       cudaStream_t st) {
+  B200_REQUIRE(front_fused_supported(tokens, L), "front: unsupported shape (tokens %d, hidden %d)",
+               tokens, L->hidden);
+  B200_REQUIRE(L->top_k <= L->experts, "front: top_k (%d) exceeds experts (%d)", L->top_k, L->experts);
+  B200_REQUIRE(h_dtype == B200MOE_DT_F32 || h_dtype == B200MOE_DT_BF16,
+               "front: activations must be fp32 or bf16");
+  static std::atomic<unsigned> next_slot{0};
+  unsigned* base = front_sync_base();
+  if (base == nullptr) return B200MOE_ERR_CUDA;
+  unsigned* sync = base + 2 * (next_slot.fetch_add(1) % FRONT_SYNC_SLOTS);
+  int d = L->hidden, E = L->experts, k = L->top_k;
+  float eps = L->rms_epsilon;
+  const float* norm_w = L->ffn_norm_weight;
+  const float* rw = L->router_weight;
+  const float* rb = L->router_bias;
+  uint4* xs4 = static_cast<uint4*>(xs);
+  void* args[] = {&h, &d, &E, &k, &eps, &norm_w, &rw, &rb, &experts, &gates, &counts, &seg,
+                  &perm, &inv, &kperm, &xs4, &sync, &status};
+  const void* fn = h_dtype == B200MOE_DT_F32
+                       ? reinterpret_cast<const void*>(&front_fused_kernel<float>)
+                       : reinterpret_cast<const void*>(&front_fused_kernel<__nv_bfloat16>);
+  B200_CHECK_CUDA(cudaLaunchCooperativeKernel(fn, dim3(tokens), dim3(RB_THREADS), args, 0, st));
+  return B200MOE_OK;
+}
+
+int clear_front_sync(cudaStream_t st) {
+  unsigned* base = front_sync_base();
+  if (base == nullptr) return B200MOE_ERR_CUDA;
+  B200_CHECK_CUDA(cudaMemsetAsync(base, 0, sizeof(unsigned) * 2 * FRONT_SYNC_SLOTS, st));
+  return B200MOE_OK;
 }
 
 int launch_router(const void* h, int h_dtype, int tokens, const b200moe_layer_t* L, void* xn,

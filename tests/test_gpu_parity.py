@@ -400,3 +400,47 @@ def test_quantized_dense_linear_through_the_registry(M, kind, rows):
     assert got.shape == (2, rows, n)
     assert orc.rel_l2(got.cpu(), want) < 5e-3
     assert orc.rel_l2(got2.cpu(), want - bias) < 5e-3
+
+
+# ------------------------------------------------ fused decode front end
+@pytest.mark.parametrize("name,tokens", [("small_q8", 1), ("small_q8", 7), ("small_q8", 40),
+                                         ("small_top4", 29), ("small_grok", 128), ("small_dense", 21)])
+@pytest.mark.parametrize("kperm", [0, 1])
+def test_fused_front_equals_the_three_staged_kernels(M, name, tokens, kperm):
+    """b200moe_front against b200moe_router + b200moe_route_plan +
+    b200moe_permute_rows: every output bit-equal; called twice in a row (its
+    grid barrier resets itself)."""
+    from shark_platform_b200 import _cabi as C
+
+    case = syn.make_case(syn.CASES[name], tokens=tokens)
+    layer = b200_block(case).layer
+    h = device_input(case).reshape(tokens, -1).contiguous()
+    dt = C.DT_BF16 if h.dtype == torch.bfloat16 else C.DT_F32
+    E, k, d = layer.expert_count, layer.top_k, layer.hidden
+    pairs = tokens * k
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    desc = ctypes.byref(layer.desc)
+    assert C.lib.b200moe_front_supported(tokens, desc) == 1
+    assert C.lib.b200moe_front_supported(129, desc) == 0 and C.lib.b200moe_front_supported(0, desc) == 0
+
+    def bufs():
+        i32 = lambda n: torch.full((n,), -7, dtype=torch.int32, device="cuda")
+        return dict(experts=i32(pairs), gates=torch.zeros(pairs, device="cuda"), counts=i32(E), seg=i32(E + 1),
+                    perm=i32(pairs), inv=i32(pairs),
+                    xs=torch.zeros(pairs, d, dtype=torch.float16, device="cuda"))
+
+    a = bufs()
+    xn = torch.empty(tokens, d, dtype=torch.float16, device="cuda")
+    C.check(C.lib.b200moe_router(p(h), dt, tokens, desc, p(xn), p(a["experts"]), p(a["gates"]), st))
+    C.check(C.lib.b200moe_route_plan(p(a["experts"]), pairs, 0, E, p(a["counts"]), p(a["seg"]), p(a["perm"]),
+                                     p(a["inv"]), st))
+    C.check(C.lib.b200moe_permute_rows(p(xn), p(a["perm"]), p(a["seg"]), E, pairs, k, d, kperm, p(a["xs"]), st))
+    for _ in range(2):
+        b = bufs()
+        C.check(C.lib.b200moe_front(p(h), dt, tokens, desc, kperm, p(b["experts"]), p(b["gates"]), p(b["counts"]),
+                                    p(b["seg"]), p(b["perm"]), p(b["inv"]), p(b["xs"]), st))
+        torch.cuda.synchronize()
+        assert M.device_status() == 0
+        for key in a:
+            assert torch.equal(a[key], b[key]), key
