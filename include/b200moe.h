@@ -191,7 +191,7 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
  * B200MOE_REGIME_STREAM) (e.g. 128 pairs at d = 4096); larger calls fail with
  * B200MOE_ERR_INVALID and a message.  Calls no cudaMalloc / cudaFree.
  * The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress): make that first call outside any stream capture.
+ * (cudaGetSymbolAddress); later calls reuse it.
  * All calls share the one array and nothing in it needs clearing between
  * calls (every partial that is read was written by the same call), but two
  * calls that overlap on the GPU (different streams) race on it. */
