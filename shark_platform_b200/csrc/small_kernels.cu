@@ -317,7 +317,7 @@ constexpr int FRONT_PAIRS_PER_THREAD = FRONT_MAX_PAIRS / RB_THREADS;
 constexpr int FRONT_SYNC_SLOTS = 32;
 
 // {arrived, departed} per slot; zero between launches (the last CTA to leave
-// the barrier resets its slot).  The host hands slots out round-robin, so up to
+// the barrier resets its slot).  The host hands slots out in rotation, so up to
 // FRONT_SYNC_SLOTS launches may be in flight on one device.
 __device__ unsigned g_front_sync[FRONT_SYNC_SLOTS][2];
 
