@@ -444,3 +444,59 @@ def test_fused_front_equals_the_three_staged_kernels(M, name, tokens, kperm):
         assert M.device_status() == 0
         for key in a:
             assert torch.equal(a[key], b[key]), key
+
+
+# ------------------------------------------------ model patching
+class _FakeNorm(torch.nn.Module):
+    def __init__(self, epsilon):
+        super().__init__()
+        self.epsilon = epsilon
+
+
+class _FakeExperts(torch.nn.Module):
+    def __init__(self, activation):
+        super().__init__()
+        self.activation = activation
+
+
+class _FakeMoeBlock(torch.nn.Module):
+    """The attributes sharktank's MoeBlock carries
+    (layers/mixture_of_experts_block.py:31-62); its forward is never reached."""
+
+    def __init__(self, theta, expert_count, expert_used_count, eps, activation):
+        super().__init__()
+        self.theta = theta
+        self.expert_count = expert_count
+        self.expert_used_count = expert_used_count
+        self.ffn_norm = _FakeNorm(eps)
+        self.experts = _FakeExperts(activation)
+
+    def forward(self, h):
+        raise AssertionError("the reference block should have been replaced")
+
+
+def test_patch_moe_blocks_swaps_every_block(M):
+    import torch.nn.functional as F
+
+    from shark_platform_b200 import plugin
+    from shark_platform_b200.moe import B200MoeBlock
+
+    cases = [syn.make_case(syn.CASES[n]) for n in ("small_q8", "small_grok")]
+    acts = [F.silu, F.gelu]
+
+    class Model(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.moe_blocks = torch.nn.ModuleList(
+                _FakeMoeBlock(mirror_theta(c), c.spec.experts, c.spec.top_k, c.spec.eps, a)
+                for c, a in zip(cases, acts))
+            self.head = torch.nn.Linear(4, 4)
+
+    model = Model()
+    assert plugin.patch_moe_blocks(model) == 2
+    assert all(isinstance(b, B200MoeBlock) for b in model.moe_blocks)
+    assert isinstance(model.head, torch.nn.Linear)
+    assert plugin.patch_moe_blocks(model) == 0  # idempotent
+    for blk, case in zip(model.moe_blocks, cases):
+        want = b200_block(case)(device_input(case))
+        assert torch.equal(blk(device_input(case)), want)

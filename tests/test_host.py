@@ -197,3 +197,11 @@ def test_entry_points_reject_bad_arguments_without_touching_the_gpu():
     assert rc == -1 and "out of range" in C.last_error()
     with pytest.raises(C.B200MoeError):
         C.check(rc, "ep_barrier")
+
+
+def test_patch_moe_blocks_leaves_other_modules_alone():
+    from shark_platform_b200 import plugin
+
+    model = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.ReLU())
+    assert plugin.patch_moe_blocks(model) == 0
+    assert isinstance(model[0], torch.nn.Linear)
