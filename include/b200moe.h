@@ -39,7 +39,8 @@ enum {
 
 enum { B200MOE_ACT_SILU = 0, B200MOE_ACT_GELU = 1 }; /* F.silu | F.gelu (erf) */
 enum { B200MOE_DT_F32 = 0, B200MOE_DT_F16 = 1, B200MOE_DT_BF16 = 2 };
-enum { B200MOE_REGIME_AUTO = 0, B200MOE_REGIME_STREAM = 1, B200MOE_REGIME_TENSOR = 2 };
+enum { B200MOE_REGIME_AUTO = 0, B200MOE_REGIME_STREAM = 1, B200MOE_REGIME_TENSOR = 2,
+       B200MOE_REGIME_TENSOR_PAIR = 3 /* tensor kernel on CTA pairs; explicit only */ };
 
 /* One stacked expert weight tensor `ffn_{gate,up,down}_exps.weight`,
  * logical shape [experts, rows, cols] with cols (the reduction dim) innermost

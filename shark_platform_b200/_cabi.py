@@ -17,7 +17,7 @@ HEADER_PATH = os.path.join(os.path.dirname(HERE), "include", "b200moe.h")
 LAYOUT_Q8_0, LAYOUT_Q4_K, LAYOUT_F16 = 0, 1, 2
 ACT_SILU, ACT_GELU = 0, 1
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
-REGIME_AUTO, REGIME_STREAM, REGIME_TENSOR = 0, 1, 2
+REGIME_AUTO, REGIME_STREAM, REGIME_TENSOR, REGIME_TENSOR_PAIR = 0, 1, 2, 3
 
 
 class B200MoeError(RuntimeError):

@@ -130,6 +130,7 @@ constexpr int TENSOR_MIN_TOKENS = 97;
 int pick_regime(int regime, const b200moe_weight_t* w, int max_segment) {
   const bool can_tensor = w != nullptr && tc_supported(w);
   if (regime == B200MOE_REGIME_TENSOR) return B200MOE_REGIME_TENSOR;
+  if (regime == B200MOE_REGIME_TENSOR_PAIR) return B200MOE_REGIME_TENSOR_PAIR;
   if (regime == B200MOE_REGIME_STREAM) return B200MOE_REGIME_STREAM;
   return (can_tensor && max_segment >= TENSOR_MIN_TOKENS) ? B200MOE_REGIME_TENSOR
                                                           : B200MOE_REGIME_STREAM;
@@ -330,6 +331,9 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
   B200_REQUIRE(activation == B200MOE_ACT_SILU || activation == B200MOE_ACT_GELU,
                "gate_up: unknown activation %d", activation);
   const int r = pick_regime(regime, gate, max_segment);
+  if (r == B200MOE_REGIME_TENSOR_PAIR)
+    return launch_tc_pair_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, out_kperm, a_out,
+                                  static_cast<cudaStream_t>(stream));
   if (r == B200MOE_REGIME_TENSOR) {
     return launch_tc_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, out_kperm, a_out,
                              static_cast<cudaStream_t>(stream));
@@ -341,8 +345,9 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
 int b200moe_down_ksplit(const b200moe_weight_t* down, int32_t pairs, int32_t max_segment,
                         int regime) {
   if (down == nullptr) return 1;
-  if (pick_regime(regime, down, max_segment) == B200MOE_REGIME_TENSOR)
-    return tc_down_ksplit(down, pairs);
+  const int r = pick_regime(regime, down, max_segment);
+  if (r == B200MOE_REGIME_TENSOR_PAIR) return 1;
+  if (r == B200MOE_REGIME_TENSOR) return tc_down_ksplit(down, pairs);
   return stream_down_ksplit(down, pairs);
 }
 
@@ -353,6 +358,9 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
   B200_REQUIRE(pairs == 0 || (a && d_out), "down: NULL buffer");
   B200_REQUIRE(ksplit >= 1, "down: ksplit must come from b200moe_down_ksplit");
   const int r = pick_regime(regime, down, max_segment);
+  if (r == B200MOE_REGIME_TENSOR_PAIR)
+    return launch_tc_pair_down(a, seg_offsets, pairs, 192, down, ksplit, d_out,
+                               static_cast<cudaStream_t>(stream));
   if (r == B200MOE_REGIME_TENSOR)
     return launch_tc_down(a, seg_offsets, pairs, 192, down, ksplit, d_out,
                           static_cast<cudaStream_t>(stream));

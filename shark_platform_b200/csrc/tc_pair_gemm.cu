@@ -1,8 +1,9 @@
 // CTA-pair variant of the tensor-core grouped expert GEMM (tcgen05, cta_group::2).
 //
-// STATUS: written and compile-checked only; it has not run on a GPU yet.  Not
-// part of the library build.  First run: one GPU, small shapes, compare with
-// tc_gemm_kernel bit for bit (same accumulation order per output element).
+// STATUS: written and compile-checked only; it has not run on a GPU yet.
+// Reached only with regime B200MOE_REGIME_TENSOR_PAIR (never chosen by auto).
+// First run: one GPU, small shapes, compare with tc_gemm_kernel bit for bit
+// (same accumulation order per output element).
 //
 // Why: tc_gemm_kernel (one CTA per 256 weight rows x 192 tokens) is bound by
 // what one SM can ingest: per 64-k stage 16 KB of quantised weights + 24 KB of
@@ -29,6 +30,7 @@
 //   * MMA N must be a multiple of 32 (each CTA holds N/2 rows, a multiple of 16)
 // No TMA load uses cluster multicast.
 #include "common.cuh"
+#include "kernels.h"
 
 namespace b200moe {
 namespace {

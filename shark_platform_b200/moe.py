@@ -29,7 +29,8 @@ from . import _cabi as C
 from . import ops as _ops
 
 _DT = {torch.float32: C.DT_F32, torch.float16: C.DT_F16, torch.bfloat16: C.DT_BF16}
-REGIMES = {"auto": C.REGIME_AUTO, "stream": C.REGIME_STREAM, "tensor": C.REGIME_TENSOR}
+REGIMES = {"auto": C.REGIME_AUTO, "stream": C.REGIME_STREAM, "tensor": C.REGIME_TENSOR,
+           "tensor_pair": C.REGIME_TENSOR_PAIR}
 
 
 def _ptr(t: Optional[torch.Tensor]):
