@@ -330,7 +330,10 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
   B200_REQUIRE(pairs == 0 || (xs && a_out), "gate_up: NULL buffer");
   B200_REQUIRE(activation == B200MOE_ACT_SILU || activation == B200MOE_ACT_GELU,
                "gate_up: unknown activation %d", activation);
-  const int r = pick_regime(regime, gate, max_segment);
+  int r = pick_regime(regime, gate, max_segment);
+  // shapes the pair kernel cannot tile go to the single-CTA tensor kernel
+  if (r == B200MOE_REGIME_TENSOR_PAIR && !(tc_pair_supported_gate_up(gate) && tc_pair_supported_gate_up(up)))
+    r = B200MOE_REGIME_TENSOR;
   if (r == B200MOE_REGIME_TENSOR_PAIR)
     return launch_tc_pair_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, out_kperm, a_out,
                                   static_cast<cudaStream_t>(stream));
@@ -345,7 +348,8 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
 int b200moe_down_ksplit(const b200moe_weight_t* down, int32_t pairs, int32_t max_segment,
                         int regime) {
   if (down == nullptr) return 1;
-  const int r = pick_regime(regime, down, max_segment);
+  int r = pick_regime(regime, down, max_segment);
+  if (r == B200MOE_REGIME_TENSOR_PAIR && !tc_pair_supported_down(down)) r = B200MOE_REGIME_TENSOR;
   if (r == B200MOE_REGIME_TENSOR_PAIR) return 1;
   if (r == B200MOE_REGIME_TENSOR) return tc_down_ksplit(down, pairs);
   return stream_down_ksplit(down, pairs);
@@ -357,7 +361,8 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
   B200_REQUIRE(down && seg_offsets, "down: NULL argument");
   B200_REQUIRE(pairs == 0 || (a && d_out), "down: NULL buffer");
   B200_REQUIRE(ksplit >= 1, "down: ksplit must come from b200moe_down_ksplit");
-  const int r = pick_regime(regime, down, max_segment);
+  int r = pick_regime(regime, down, max_segment);
+  if (r == B200MOE_REGIME_TENSOR_PAIR && !tc_pair_supported_down(down)) r = B200MOE_REGIME_TENSOR;
   if (r == B200MOE_REGIME_TENSOR_PAIR)
     return launch_tc_pair_down(a, seg_offsets, pairs, 192, down, ksplit, d_out,
                                static_cast<cudaStream_t>(stream));
