@@ -196,6 +196,109 @@ __device__ __forceinline__ void router_select(const float* logit, int lane, int 
   }
 }
 
+// Prefill: four tokens per warp.  With one token per warp every warp streams
+// the whole router weight (E x d fp32) out of L2 for itself, 4096 tokens x 128 KB
+// for a Mixtral layer; sharing each weight vector between four tokens cuts that
+// to a quarter.  Per token the operations and their order are those of
+// router_kernel, so experts and gates are bit-identical.
+constexpr int RM_WARPS = 4;
+constexpr int RM_TOK = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(RM_WARPS * 32)
+router_multi_kernel(const T* __restrict__ h, int tokens, int d, int E, int k, float eps,
+                    const float* __restrict__ norm_w, const float* __restrict__ rw,
+                    const float* __restrict__ rb, __half* __restrict__ xn_out,
+                    int32_t* __restrict__ experts_out, float* __restrict__ gates_out) {
+  __shared__ float s_logit[RM_WARPS][RM_TOK][MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = (blockIdx.x * RM_WARPS + warp) * RM_TOK;
+  if (t0 >= tokens) return;
+  const int nt = min(RM_TOK, tokens - t0);
+
+  float rstd[RM_TOK];
+  {
+    float ss[RM_TOK];
+#pragma unroll
+    for (int q = 0; q < RM_TOK; ++q) ss[q] = 0.f;
+    for (int j = lane * 8; j < d; j += 256) {
+#pragma unroll
+      for (int q = 0; q < RM_TOK; ++q) {
+        if (q < nt) {
+          float v[8];
+          load8<T>(h + static_cast<size_t>(t0 + q) * d + j, v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss[q] = fmaf(v[i], v[i], ss[q]);
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < RM_TOK; ++q) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss[q] += __shfl_xor_sync(0xffffffffu, ss[q], o);
+      rstd[q] = 1.0f / sqrtf(ss[q] / static_cast<float>(d) + eps);
+    }
+  }
+
+  for (int e0 = 0; e0 < E; e0 += 8) {
+    float acc[RM_TOK][8];
+#pragma unroll
+    for (int q = 0; q < RM_TOK; ++q)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
+    for (int j = lane * 8; j < d; j += 256) {
+      float w[8], v[RM_TOK][8];
+      load8<float>(norm_w + j, w);
+#pragma unroll
+      for (int q = 0; q < RM_TOK; ++q) {
+        if (q < nt) {
+          load8<T>(h + static_cast<size_t>(t0 + q) * d + j, v[q]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[q][i] = w[i] * (v[q][i] * rstd[q]);
+          if (e0 == 0) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              packed[i] = h2_as_u32(__halves2half2(to_half_sat(v[q][2 * i]), to_half_sat(v[q][2 * i + 1])));
+            *reinterpret_cast<uint4*>(xn_out + static_cast<size_t>(t0 + q) * d + j) =
+                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[q][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (e0 + e < E) {
+          float r[8];
+          load8<float>(rw + static_cast<size_t>(e0 + e) * d + j, r);
+#pragma unroll
+          for (int q = 0; q < RM_TOK; ++q)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[q][e] = fmaf(v[q][i], r[i], acc[q][e]);
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < RM_TOK; ++q) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[q][e] += __shfl_xor_sync(0xffffffffu, acc[q][e], o);
+        if (lane == 0 && e0 + e < E) s_logit[warp][q][e0 + e] = acc[q][e] + (rb ? rb[e0 + e] : 0.f);
+      }
+    }
+  }
+  __syncwarp();
+#pragma unroll
+  for (int q = 0; q < RM_TOK; ++q) {
+    if (q < nt)
+      router_select(s_logit[warp][q], lane, E, k, experts_out + static_cast<size_t>(t0 + q) * k,
+                    gates_out + static_cast<size_t>(t0 + q) * k);
+  }
+}
+
 // One CTA per token: used for small token counts (decode), where a warp per
 // token leaves most of the GPU idle.  The row stays in registers between the
 // two passes (hidden <= 8192).
@@ -530,6 +633,22 @@ int launch_router(const void* h, int h_dtype, int tokens, const b200moe_layer_t*
           static_cast<const __nv_bfloat16*>(h), L->hidden, L->experts, L->top_k, L->rms_epsilon,
           L->ffn_norm_weight, L->router_weight, L->router_bias, static_cast<__half*>(xn), experts,
           gates);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return B200MOE_OK;
+  }
+  if (tokens >= 1024) {
+    const int per_cta = RM_WARPS * RM_TOK;
+    dim3 mgrid((tokens + per_cta - 1) / per_cta), mblock(RM_WARPS * 32);
+    if (h_dtype == B200MOE_DT_F32)
+      router_multi_kernel<float><<<mgrid, mblock, 0, st>>>(
+          static_cast<const float*>(h), tokens, L->hidden, L->experts, L->top_k, L->rms_epsilon,
+          L->ffn_norm_weight, L->router_weight, L->router_bias, static_cast<__half*>(xn), experts,
+          gates);
+    else
+      router_multi_kernel<__nv_bfloat16><<<mgrid, mblock, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(h), tokens, L->hidden, L->experts, L->top_k,
+          L->rms_epsilon, L->ffn_norm_weight, L->router_weight, L->router_bias,
+          static_cast<__half*>(xn), experts, gates);
     B200_CHECK_CUDA(cudaGetLastError());
     return B200MOE_OK;
   }
