@@ -287,15 +287,17 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
     s_seg[args.E] = args.seg[args.E];
     s_prefix[args.E] = run;
   }
+  __syncthreads();
+  // the peer must be running, with its barriers initialised, before anything is
+  // signalled across CTAs and before the pair allocates tensor memory together
+  cluster_arrive();
+  cluster_wait();
   if (warp == TP_WARP_MMA) {
     tmem_alloc2(smem_u32(&s_tmem), 512);
     tmem_relinquish2();
   }
   tp_fence_before();
   __syncthreads();
-  // the peer's barriers must exist before anything is signalled across CTAs
-  cluster_arrive();
-  cluster_wait();
   tp_fence_after();
   const uint32_t tmem = s_tmem;
   const int total_tiles = s_prefix[args.E];
