@@ -39,7 +39,8 @@ enum {
 
 enum { B200MOE_ACT_SILU = 0, B200MOE_ACT_GELU = 1 }; /* F.silu | F.gelu (erf) */
 enum { B200MOE_DT_F32 = 0, B200MOE_DT_F16 = 1, B200MOE_DT_BF16 = 2 };
-enum { B200MOE_REGIME_AUTO = 0, B200MOE_REGIME_STREAM = 1, B200MOE_REGIME_TENSOR = 2 };
+enum { B200MOE_REGIME_AUTO = 0, B200MOE_REGIME_STREAM = 1, B200MOE_REGIME_TENSOR = 2,
+       B200MOE_REGIME_TENSOR_PAIR = 3 /* tensor kernel on CTA pairs; explicit only */ };
 
 /* One stacked expert weight tensor `ffn_{gate,up,down}_exps.weight`,
  * logical shape [experts, rows, cols] with cols (the reduction dim) innermost
@@ -75,9 +76,22 @@ typedef struct {
 const char* b200moe_version(void);
 const char* b200moe_last_error(void);
 
-/* Reads and clears the device status word that kernels set when a bounded
- * wait gives up or an index check fails; synchronises the stream.  0 = clean. */
+/* Reads and clears the device status word that kernels set; synchronises the
+ * stream.  Bits: 1 a bounded wait gave up, 2 an index check failed (the access
+ * was skipped), 4 tensor memory could not be obtained, 8 an expert-GEMM operand
+ * act(gate)*up was outside the fp16 range and was clipped to +-65504.  Bits 1, 2
+ * and 4 make the call return B200MOE_ERR_DEVICE; bit 8 alone is a warning: the
+ * call returns B200MOE_OK and *status_out carries it, so that a checkpoint with
+ * activation outliers cannot clip unnoticed.  (The normalised activations
+ * cannot leave the fp16 range: |x * rsqrt(mean x^2)| <= sqrt(d).)  0 = clean. */
 int b200moe_device_status(void* stream, int32_t* status_out);
+
+/* How long the cross-GPU barrier (b200moe_ep_barrier) spins before it gives up,
+ * in GPU clock ticks; 0 restores the default of 2^32 ticks (about two seconds).
+ * Process-wide, takes effect for launches made after the call.  No reference
+ * counterpart.  Meant for tests and for hosts that want to notice a lost peer
+ * sooner; too small a value turns ordinary skew between ranks into errors. */
+int b200moe_set_wait_limit(int64_t clock_ticks);
 
 /* layout.dequant() of one weight tensor, bit-exact (types/layouts.py:274-290
  * for Q8_0: fp16(d*q) or the exact fp32 product; types/layouts.py:505-517 for
@@ -194,7 +208,9 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
  * (cudaGetSymbolAddress); later calls reuse it.
  * All calls share the one array and nothing in it needs clearing between
  * calls (every partial that is read was written by the same call), but two
- * calls that overlap on the GPU (different streams) race on it. */
+ * calls that overlap on the GPU (different streams) race on it.  The host-side
+ * lookup of the array's address is not synchronised either: make the first call
+ * on a device from one thread before other threads use this entry point. */
 int b200moe_down_noalloc(const void* a, const int32_t* seg_offsets, int32_t pairs,
                          int32_t max_segment, const b200moe_weight_t* down, float* d_out,
                          void* stream);

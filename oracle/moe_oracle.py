@@ -233,6 +233,53 @@ def dequant(kind: str, planes: dict) -> np.ndarray:
     raise ValueError(kind)
 
 
+# The same two dequantisations with torch's multi-threaded CPU operators, for
+# full-size layers (hundreds of millions of weights per matrix, where the numpy
+# versions above take minutes).  tests/test_oracle.py checks them bit for bit
+# against the numpy versions, which are the ones pinned to the reference.
+
+
+def q8_0_dequant_torch(planes: dict) -> torch.Tensor:
+    """BlockScaledLayout.dequant (types/layouts.py:274-290) on torch tensors:
+    fp16(d * q), the product formed exactly in fp32 and rounded once."""
+    d, qs = planes["d"], planes["qs"]
+    out = (d.to(torch.float32) * qs.to(torch.float32)).to(torch.float16)
+    return out.reshape(*out.shape[:-2], out.shape[-2] * out.shape[-1])
+
+
+def _unpack_i4_torch(b: torch.Tensor) -> torch.Tensor:
+    b = b.view(torch.uint8)
+    return torch.stack([b & 0xF, b >> 4], dim=-1).reshape(*b.shape[:-1], b.shape[-1] * 2)
+
+
+def _unpack_i6_torch(high2: torch.Tensor, low4: torch.Tensor) -> torch.Tensor:
+    lo = _unpack_i4_torch(low4)
+    h = high2.view(torch.uint8)
+    hi = torch.stack([(h >> (2 * f)) & 3 for f in range(4)], dim=-1).reshape(*h.shape[:-1], h.shape[-1] * 4)
+    return lo | (hi << 4)
+
+
+def q4_k_dequant_torch(planes: dict) -> torch.Tensor:
+    """SuperBlockOffsetScaled_4_6_Layout.dequant (types/layouts.py:505-517) on
+    torch tensors, one fp16 rounding after each of the four operations."""
+    sc = _unpack_i6_torch(planes["sb_scales_high"], planes["sb_scales_low"]).to(torch.float32)
+    mn = _unpack_i6_torch(planes["sb_mins_high"], planes["sb_mins_low"]).to(torch.float32)
+    q = _unpack_i4_torch(planes["qs"]).to(torch.float32)  # [.., SUP, 8, 32]
+    h = lambda a: a.to(torch.float16).to(torch.float32)
+    t1 = h(planes["d"].to(torch.float32) * sc).unsqueeze(-1)
+    t2 = h(planes["dmin"].to(torch.float32) * mn).unsqueeze(-1)
+    w = (h(t1 * q) - t2).to(torch.float16)
+    return w.reshape(*w.shape[:-3], w.shape[-3] * 256)
+
+
+def dequant_torch(kind: str, planes: dict) -> torch.Tensor:
+    if kind == Q8_0:
+        return q8_0_dequant_torch(planes)
+    if kind == Q4_K:
+        return q4_k_dequant_torch(planes)
+    raise ValueError(kind)
+
+
 # --------------------------------------------------------------------------
 # Layer stages (sharktank/layers/mixture_of_experts_block.py,
 # layers/ffn_moe_block.py, ops/default_impls.py)
@@ -393,6 +440,39 @@ def moe_block(h: torch.Tensor, p: MoeParams, form: str = "pregather", chunk: int
     if p.out_norm_w is not None:
         y = rms_norm(y, p.out_norm_w, p.eps)
     return h + y, {"xn": xn, "gate": gate, "experts": idx, "prob": prob}
+
+
+def moe_block_sampled(h: torch.Tensor, p: MoeParams, expert_weights: Callable, token_index: torch.Tensor):
+    """MoeBlock.forward (mixture_of_experts_block.py:64-90) for layers too large
+    to hold dequantised: norm and router for EVERY token, the expert FFN (the
+    per-expert form, `experts_per_expert`) only for the tokens in `token_index`,
+    with the dense weights of one expert at a time fetched through
+    `expert_weights(e) -> (w_gate[N,K], w_up[N,K], w_down[d,F])`.  `p.w_*` are
+    ignored.  Returns (output rows [len(token_index), d], intermediates of all
+    tokens).  Tokens are independent, so the sampled rows equal the same rows
+    of the full evaluation."""
+    bs, sl, d = h.shape
+    xn = rms_norm(h, p.norm_w, p.eps).view(-1, d)
+    gate, idx, prob = router(xn, p.router_w, p.router_b, p.top_k)
+    act = ACTIVATIONS[p.activation]
+    tok_sel = token_index.to(torch.int64)
+    xs, ex_s, g_s = xn[tok_sel], idx[tok_sel], gate[tok_sel]
+    parts = torch.zeros(tok_sel.numel(), p.top_k, d, dtype=xn.dtype)
+    n_experts = p.router_w.shape[0]
+    for e in range(n_experts):
+        tok, slot = torch.nonzero(ex_s == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        wg, wu, wd = expert_weights(e)
+        x = xs[tok]
+        a = act(x @ wg.to(x.dtype).mT) * (x @ wu.to(x.dtype).mT)
+        parts[tok, slot] = (a @ wd.to(x.dtype).mT) * g_s[tok, slot].unsqueeze(1)
+        del wg, wu, wd
+    y = parts.sum(dim=1)
+    if p.out_norm_w is not None:
+        y = rms_norm(y, p.out_norm_w, p.eps)
+    out = h.view(-1, d)[tok_sel] + y
+    return out, {"xn": xn, "gate": gate, "experts": idx, "prob": prob}
 
 
 def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:

@@ -17,7 +17,7 @@ HEADER_PATH = os.path.join(os.path.dirname(HERE), "include", "b200moe.h")
 LAYOUT_Q8_0, LAYOUT_Q4_K, LAYOUT_F16 = 0, 1, 2
 ACT_SILU, ACT_GELU = 0, 1
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
-REGIME_AUTO, REGIME_STREAM, REGIME_TENSOR = 0, 1, 2
+REGIME_AUTO, REGIME_STREAM, REGIME_TENSOR, REGIME_TENSOR_PAIR = 0, 1, 2, 3
 
 
 class B200MoeError(RuntimeError):
@@ -91,6 +91,7 @@ _PROTOS = {
     "b200moe_version": (c_char_p, []),
     "b200moe_last_error": (c_char_p, []),
     "b200moe_device_status": (c_int, [_P, POINTER(c_int32)]),
+    "b200moe_set_wait_limit": (c_int, [c_int64]),
     "b200moe_dequant": (c_int, [_W, c_int, _P, _P]),
     "b200moe_q4k_prepare": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, _P, _P]),
     "b200moe_q8_prepare": (c_int, [_P, c_int64, c_int32, _P, _P]),

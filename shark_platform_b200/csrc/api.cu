@@ -127,10 +127,14 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // weight-streaming kernel (where the layout allows it).
 constexpr int TENSOR_MIN_TOKENS = 97;
 
-int pick_regime(int regime, const b200moe_weight_t* w, int max_segment) {
-  const bool can_tensor = w != nullptr && tc_supported(w);
+// `down` says which of the two products the weight belongs to (their tile
+// shapes differ).  An explicit regime is taken as given and fails in the
+// launcher when the shape does not fit; AUTO only picks what can run.
+int pick_regime(int regime, const b200moe_weight_t* w, int max_segment, bool down) {
   if (regime == B200MOE_REGIME_TENSOR) return B200MOE_REGIME_TENSOR;
+  if (regime == B200MOE_REGIME_TENSOR_PAIR) return B200MOE_REGIME_TENSOR_PAIR;
   if (regime == B200MOE_REGIME_STREAM) return B200MOE_REGIME_STREAM;
+  const bool can_tensor = w != nullptr && tc_supported(w, down);
   return (can_tensor && max_segment >= TENSOR_MIN_TOKENS) ? B200MOE_REGIME_TENSOR
                                                           : B200MOE_REGIME_STREAM;
 }
@@ -155,7 +159,7 @@ Workspace carve(const b200moe_layer_t* L, int tokens, void* base) {
   const size_t P = T * L->top_k;
   const size_t d = L->hidden, F = L->ffn;
   int ks = stream_down_ksplit(&L->down, static_cast<int>(P));
-  if (tc_supported(&L->down)) ks = max(ks, tc_down_ksplit(&L->down, static_cast<int>(P)));
+  if (tc_supported(&L->down, true)) ks = max(ks, tc_down_ksplit(&L->down, static_cast<int>(P)));
   uint8_t* p = static_cast<uint8_t*>(base);
   size_t off = 0;
   auto take = [&](size_t n) {
@@ -226,10 +230,11 @@ int b200moe_device_status(void* stream, int32_t* status_out) {
   B200_CHECK_CUDA(cudaMemsetAsync(p, 0, sizeof(v), st));
   B200_CHECK_CUDA(cudaStreamSynchronize(st));
   if (status_out) *status_out = v;
-  if (v != 0) {
+  if ((v & DEV_ERR_MASK) != 0) {
     clear_front_sync(st);  // a timed-out grid barrier leaves its counters behind
     cudaStreamSynchronize(st);
-    set_error("device status word = %d (1: bounded wait timed out, 2: bounds check, 4: tmem)", v);
+    set_error("device status word = %d (1: bounded wait timed out, 2: bounds check, 4: tmem, "
+              "8: fp16 operand clipped)", v);
     return B200MOE_ERR_DEVICE;
   }
   return B200MOE_OK;
@@ -329,7 +334,13 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
   B200_REQUIRE(pairs == 0 || (xs && a_out), "gate_up: NULL buffer");
   B200_REQUIRE(activation == B200MOE_ACT_SILU || activation == B200MOE_ACT_GELU,
                "gate_up: unknown activation %d", activation);
-  const int r = pick_regime(regime, gate, max_segment);
+  int r = pick_regime(regime, gate, max_segment, false);
+  // shapes the pair kernel cannot tile go to the single-CTA tensor kernel
+  if (r == B200MOE_REGIME_TENSOR_PAIR && !(tc_pair_supported_gate_up(gate) && tc_pair_supported_gate_up(up)))
+    r = B200MOE_REGIME_TENSOR;
+  if (r == B200MOE_REGIME_TENSOR_PAIR)
+    return launch_tc_pair_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, out_kperm, a_out,
+                                  static_cast<cudaStream_t>(stream));
   if (r == B200MOE_REGIME_TENSOR) {
     return launch_tc_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, out_kperm, a_out,
                              static_cast<cudaStream_t>(stream));
@@ -341,8 +352,10 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
 int b200moe_down_ksplit(const b200moe_weight_t* down, int32_t pairs, int32_t max_segment,
                         int regime) {
   if (down == nullptr) return 1;
-  if (pick_regime(regime, down, max_segment) == B200MOE_REGIME_TENSOR)
-    return tc_down_ksplit(down, pairs);
+  int r = pick_regime(regime, down, max_segment, true);
+  if (r == B200MOE_REGIME_TENSOR_PAIR && !tc_pair_supported_down(down)) r = B200MOE_REGIME_TENSOR;
+  if (r == B200MOE_REGIME_TENSOR_PAIR) return 1;
+  if (r == B200MOE_REGIME_TENSOR) return tc_down_ksplit(down, pairs);
   return stream_down_ksplit(down, pairs);
 }
 
@@ -352,7 +365,11 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
   B200_REQUIRE(down && seg_offsets, "down: NULL argument");
   B200_REQUIRE(pairs == 0 || (a && d_out), "down: NULL buffer");
   B200_REQUIRE(ksplit >= 1, "down: ksplit must come from b200moe_down_ksplit");
-  const int r = pick_regime(regime, down, max_segment);
+  int r = pick_regime(regime, down, max_segment, true);
+  if (r == B200MOE_REGIME_TENSOR_PAIR && !tc_pair_supported_down(down)) r = B200MOE_REGIME_TENSOR;
+  if (r == B200MOE_REGIME_TENSOR_PAIR)
+    return launch_tc_pair_down(a, seg_offsets, pairs, 192, down, ksplit, d_out,
+                               static_cast<cudaStream_t>(stream));
   if (r == B200MOE_REGIME_TENSOR)
     return launch_tc_down(a, seg_offsets, pairs, 192, down, ksplit, d_out,
                           static_cast<cudaStream_t>(stream));

@@ -50,6 +50,8 @@ enum : int32_t {
   DEV_ERR_WAIT_TIMEOUT = 1,  // a bounded mbarrier wait gave up
   DEV_ERR_BOUNDS = 2,        // an index check failed; the access was skipped
   DEV_ERR_TMEM = 4,          // tensor-memory allocation/wait gave up
+  DEV_ERR_MASK = 7,
+  DEV_WARN_SATURATED = 8,    // an fp16 operand was clipped to +-65504 (a warning, not an error)
 };
 
 // -------------------------------------------------------------- device side
@@ -111,6 +113,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+}
+
+// The same wait for a whole warp (all 32 lanes call it, converged).  Every lane
+// runs its own bounded wait, so all of them come back; the vote then makes the
+// outcome uniform: when the abort flag is raised at the moment a phase completes,
+// one lane may see the phase and another the flag, and a warp that split on that
+// would meet `.sync.aligned` instructions or block-wide barriers with lanes
+// missing.  Either every lane continues or every lane gives up.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag, int32_t* status) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, status);
+  return __all_sync(0xffffffffu, ok);
 }
 
 // 2-D tiled bulk tensor load global -> shared, completion on an mbarrier.
@@ -206,6 +220,13 @@ __device__ __forceinline__ float gelu_erf_f(float x) {
 __device__ __forceinline__ __half to_half_sat(float v) {
   v = fminf(fmaxf(v, -65504.0f), 65504.0f);
   return __float2half_rn(v);
+}
+
+// The same, recording in the status word that a value was out of fp16 range
+// (|v| >= 65520 would round to infinity; NaN is passed through unflagged).
+__device__ __forceinline__ __half to_half_sat(float v, int32_t* status) {
+  if (fabsf(v) >= 65520.0f) atomicOr(status, DEV_WARN_SATURATED);
+  return to_half_sat(v);
 }
 
 #endif  // __CUDACC__

@@ -44,7 +44,8 @@ __global__ void ep_publish_kernel(EpPtrs p, const int32_t* __restrict__ counts) 
 // After the wait the caller's counts matrix is complete; thread 0 then derives
 // the local segment offsets (rows per local expert summed over sources).
 __global__ void __launch_bounds__(32)
-ep_barrier_kernel(EpPtrs p, int epoch, int32_t* __restrict__ seg2, int32_t* status) {
+ep_barrier_kernel(EpPtrs p, int epoch, int32_t* __restrict__ seg2, int32_t* status,
+                  long long limit) {
   const int s = threadIdx.x;
   if (s < p.world) {
     __threadfence_system();
@@ -56,7 +57,7 @@ ep_barrier_kernel(EpPtrs p, int epoch, int32_t* __restrict__ seg2, int32_t* stat
       int v;
       asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
       if (v - epoch >= 0) break;
-      if (clock64() - t0 > (1ll << 32)) {  // ~2 s: a peer is gone; report, do not hang
+      if (clock64() - t0 > limit) {  // default ~2 s: a peer is gone; report, do not hang
         atomicOr(status, DEV_ERR_WAIT_TIMEOUT);
         break;
       }
@@ -158,6 +159,9 @@ ep_return_kernel(EpPtrs p, const float* __restrict__ d_rows, int ksplit, int cap
   }
 }
 
+// spin limit of the cross-GPU barrier in clock ticks (b200moe_set_wait_limit)
+long long g_barrier_ticks = 1ll << 32;
+
 int fill(EpPtrs* p, const b200moe_ep_t* ep) {
   B200_REQUIRE(ep != nullptr, "ep: NULL descriptor");
   B200_REQUIRE(ep->world >= 1 && ep->world <= EP_MAX_WORLD && ep->rank >= 0 && ep->rank < ep->world,
@@ -194,12 +198,19 @@ int b200moe_ep_publish_counts(const b200moe_ep_t* ep, const int32_t* counts, voi
   return B200MOE_OK;
 }
 
+int b200moe_set_wait_limit(int64_t clock_ticks) {
+  B200_REQUIRE(clock_ticks >= 0, "set_wait_limit: negative tick count");
+  g_barrier_ticks = clock_ticks == 0 ? (1ll << 32) : static_cast<long long>(clock_ticks);
+  return B200MOE_OK;
+}
+
 int b200moe_ep_barrier(const b200moe_ep_t* ep, int32_t epoch, int32_t* seg2_out, void* stream) {
   EpPtrs p;
   if (int rc = fill(&p, ep)) return rc;
   int32_t* status = device_status_ptr();
   if (status == nullptr) return B200MOE_ERR_CUDA;
-  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, epoch, seg2_out, status);
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, epoch, seg2_out, status,
+                                                                   g_barrier_ticks);
   B200_CHECK_CUDA(cudaGetLastError());
   return B200MOE_OK;
 }

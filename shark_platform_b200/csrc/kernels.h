@@ -43,12 +43,21 @@ int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_
                        const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st);
 
 // prefill regime (tc_gemm.cu)
-bool tc_supported(const b200moe_weight_t* w);
+bool tc_supported(const b200moe_weight_t* w, bool down);
 int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_tile,
                       const b200moe_weight_t* gate, const b200moe_weight_t* up, int act,
                       int out_kperm, void* a_out, cudaStream_t st);
 int tc_down_ksplit(const b200moe_weight_t* down, int est_pairs);
 int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile,
                    const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st);
+
+// prefill regime on CTA pairs (tc_pair_gemm.cu)
+bool tc_pair_supported_gate_up(const b200moe_weight_t* gate);
+bool tc_pair_supported_down(const b200moe_weight_t* down);
+int launch_tc_pair_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_tile,
+                           const b200moe_weight_t* gate, const b200moe_weight_t* up, int act,
+                           int out_kperm, void* a_out, cudaStream_t st);
+int launch_tc_pair_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile,
+                        const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st);
 
 }  // namespace b200moe

@@ -196,6 +196,109 @@ __device__ __forceinline__ void router_select(const float* logit, int lane, int 
   }
 }
 
+// Prefill: four tokens per warp.  With one token per warp every warp streams
+// the whole router weight (E x d fp32) out of L2 for itself, 4096 tokens x 128 KB
+// for a Mixtral layer; sharing each weight vector between four tokens cuts that
+// to a quarter.  Per token the operations and their order are those of
+// router_kernel, so experts and gates are bit-identical.
+constexpr int RM_WARPS = 4;
+constexpr int RM_TOK = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(RM_WARPS * 32)
+router_multi_kernel(const T* __restrict__ h, int tokens, int d, int E, int k, float eps,
+                    const float* __restrict__ norm_w, const float* __restrict__ rw,
+                    const float* __restrict__ rb, __half* __restrict__ xn_out,
+                    int32_t* __restrict__ experts_out, float* __restrict__ gates_out) {
+  __shared__ float s_logit[RM_WARPS][RM_TOK][MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = (blockIdx.x * RM_WARPS + warp) * RM_TOK;
+  if (t0 >= tokens) return;
+  const int nt = min(RM_TOK, tokens - t0);
+
+  float rstd[RM_TOK];
+  {
+    float ss[RM_TOK];
+#pragma unroll
+    for (int q = 0; q < RM_TOK; ++q) ss[q] = 0.f;
+    for (int j = lane * 8; j < d; j += 256) {
+#pragma unroll
+      for (int q = 0; q < RM_TOK; ++q) {
+        if (q < nt) {
+          float v[8];
+          load8<T>(h + static_cast<size_t>(t0 + q) * d + j, v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss[q] = fmaf(v[i], v[i], ss[q]);
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < RM_TOK; ++q) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss[q] += __shfl_xor_sync(0xffffffffu, ss[q], o);
+      rstd[q] = 1.0f / sqrtf(ss[q] / static_cast<float>(d) + eps);
+    }
+  }
+
+  for (int e0 = 0; e0 < E; e0 += 8) {
+    float acc[RM_TOK][8];
+#pragma unroll
+    for (int q = 0; q < RM_TOK; ++q)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
+    for (int j = lane * 8; j < d; j += 256) {
+      float w[8], v[RM_TOK][8];
+      load8<float>(norm_w + j, w);
+#pragma unroll
+      for (int q = 0; q < RM_TOK; ++q) {
+        if (q < nt) {
+          load8<T>(h + static_cast<size_t>(t0 + q) * d + j, v[q]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[q][i] = w[i] * (v[q][i] * rstd[q]);
+          if (e0 == 0) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              packed[i] = h2_as_u32(__halves2half2(to_half_sat(v[q][2 * i]), to_half_sat(v[q][2 * i + 1])));
+            *reinterpret_cast<uint4*>(xn_out + static_cast<size_t>(t0 + q) * d + j) =
+                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[q][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (e0 + e < E) {
+          float r[8];
+          load8<float>(rw + static_cast<size_t>(e0 + e) * d + j, r);
+#pragma unroll
+          for (int q = 0; q < RM_TOK; ++q)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[q][e] = fmaf(v[q][i], r[i], acc[q][e]);
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < RM_TOK; ++q) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[q][e] += __shfl_xor_sync(0xffffffffu, acc[q][e], o);
+        if (lane == 0 && e0 + e < E) s_logit[warp][q][e0 + e] = acc[q][e] + (rb ? rb[e0 + e] : 0.f);
+      }
+    }
+  }
+  __syncwarp();
+#pragma unroll
+  for (int q = 0; q < RM_TOK; ++q) {
+    if (q < nt)
+      router_select(s_logit[warp][q], lane, E, k, experts_out + static_cast<size_t>(t0 + q) * k,
+                    gates_out + static_cast<size_t>(t0 + q) * k);
+  }
+}
+
 // One CTA per token: used for small token counts (decode), where a warp per
 // token leaves most of the GPU idle.  The row stays in registers between the
 // two passes (hidden <= 8192).
@@ -533,6 +636,22 @@ int launch_router(const void* h, int h_dtype, int tokens, const b200moe_layer_t*
     B200_CHECK_CUDA(cudaGetLastError());
     return B200MOE_OK;
   }
+  if (tokens >= 1024) {
+    const int per_cta = RM_WARPS * RM_TOK;
+    dim3 mgrid((tokens + per_cta - 1) / per_cta), mblock(RM_WARPS * 32);
+    if (h_dtype == B200MOE_DT_F32)
+      router_multi_kernel<float><<<mgrid, mblock, 0, st>>>(
+          static_cast<const float*>(h), tokens, L->hidden, L->experts, L->top_k, L->rms_epsilon,
+          L->ffn_norm_weight, L->router_weight, L->router_bias, static_cast<__half*>(xn), experts,
+          gates);
+    else
+      router_multi_kernel<__nv_bfloat16><<<mgrid, mblock, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(h), tokens, L->hidden, L->experts, L->top_k,
+          L->rms_epsilon, L->ffn_norm_weight, L->router_weight, L->router_bias,
+          static_cast<__half*>(xn), experts, gates);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return B200MOE_OK;
+  }
   dim3 grid((tokens + ROUTER_WARPS - 1) / ROUTER_WARPS), block(ROUTER_WARPS * 32);
   if (h_dtype == B200MOE_DT_F32) {
     router_kernel<float><<<grid, block, 0, st>>>(
@@ -749,6 +868,62 @@ __device__ __forceinline__ void store1<__nv_bfloat16>(__nv_bfloat16* p, float v)
 
 constexpr int COMBINE_THREADS = 256;
 
+// four consecutive elements at once (16-byte / 8-byte accesses)
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(raw.x << 16);
+  v[1] = __uint_as_float(raw.x & 0xffff0000u);
+  v[2] = __uint_as_float(raw.y << 16);
+  v[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&v)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+  const __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// gate-weighted sum over the token's slots for four columns; per element the
+// same operations in the same order as a scalar loop over slots and partials
+template <typename TD>
+__device__ __forceinline__ void combine4(const TD* __restrict__ dpart, int ksplit, size_t part_stride,
+                                         const int (&pos)[MAX_TOPK], const float (&gate)[MAX_TOPK],
+                                         int k, int d, int j, float (&acc)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = 0.f;
+#pragma unroll
+  for (int s = 0; s < MAX_TOPK; ++s) {
+    if (s < k && pos[s] >= 0) {
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int c = 0; c < ksplit; ++c) {
+        float p4[4];
+        load4<TD>(dpart + c * part_stride + static_cast<size_t>(pos[s]) * d + j, p4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] += p4[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] += gate[s] * v[i];
+    }
+  }
+}
+
 template <typename TD, typename TH, typename TY>
 __global__ void __launch_bounds__(COMBINE_THREADS)
 combine_kernel(const TD* __restrict__ dpart, int ksplit, size_t part_stride,
@@ -757,39 +932,40 @@ combine_kernel(const TD* __restrict__ dpart, int ksplit, size_t part_stride,
                float eps, int add_residual, TY* __restrict__ y) {
   extern __shared__ float s_row[];
   __shared__ float s_red[COMBINE_THREADS / 32];
-  const int t = blockIdx.x;
+  const size_t t = blockIdx.x;
+  int pos[MAX_TOPK];
+  float gate[MAX_TOPK];
+#pragma unroll
+  for (int s = 0; s < MAX_TOPK; ++s) {
+    pos[s] = s < k ? inv[t * k + s] : -1;
+    gate[s] = s < k ? gates[t * k + s] : 0.f;
+  }
   if (gridDim.y > 1) {
     // no output norm: column slices are independent, one slice per blockIdx.y
-    const int per = (d + gridDim.y - 1) / gridDim.y;
+    const int per = ((d / 4 + gridDim.y - 1) / gridDim.y) * 4;
     const int j0 = blockIdx.y * per, j1 = min(d, j0 + per);
-    for (int j = j0 + threadIdx.x; j < j1; j += COMBINE_THREADS) {
-      float acc = 0.f;
-      for (int s = 0; s < k; ++s) {
-        const int pos = inv[static_cast<size_t>(t) * k + s];
-        if (pos < 0) continue;
-        float v = 0.f;
-        for (int c = 0; c < ksplit; ++c)
-          v += load1<TD>(dpart + c * part_stride + static_cast<size_t>(pos) * d + j);
-        acc += gates[static_cast<size_t>(t) * k + s] * v;
+    for (int j = j0 + threadIdx.x * 4; j < j1; j += COMBINE_THREADS * 4) {
+      float acc[4];
+      combine4<TD>(dpart, ksplit, part_stride, pos, gate, k, d, j, acc);
+      if (add_residual) {
+        float r[4];
+        load4<TH>(h + t * d + j, r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] += r[i];
       }
-      if (add_residual) acc += load1<TH>(h + static_cast<size_t>(t) * d + j);
-      store1<TY>(y + static_cast<size_t>(t) * d + j, acc);
+      store4<TY>(y + t * d + j, acc);
     }
     return;
   }
   float ss = 0.f;
-  for (int j = threadIdx.x; j < d; j += COMBINE_THREADS) {
-    float acc = 0.f;
-    for (int s = 0; s < k; ++s) {
-      const int pos = inv[static_cast<size_t>(t) * k + s];
-      if (pos < 0) continue;
-      float v = 0.f;
-      for (int c = 0; c < ksplit; ++c)
-        v += load1<TD>(dpart + c * part_stride + static_cast<size_t>(pos) * d + j);
-      acc += gates[static_cast<size_t>(t) * k + s] * v;
+  for (int j = threadIdx.x * 4; j < d; j += COMBINE_THREADS * 4) {
+    float acc[4];
+    combine4<TD>(dpart, ksplit, part_stride, pos, gate, k, d, j, acc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s_row[j + i] = acc[i];
+      ss = fmaf(acc[i], acc[i], ss);
     }
-    s_row[j] = acc;
-    ss = fmaf(acc, acc, ss);
   }
   float scale = 1.f;
   if (out_norm_w != nullptr && add_residual) {
@@ -801,13 +977,21 @@ combine_kernel(const TD* __restrict__ dpart, int ksplit, size_t part_stride,
     for (int w = 0; w < COMBINE_THREADS / 32; ++w) tot += s_red[w];
     scale = 1.0f / sqrtf(tot / static_cast<float>(d) + eps);
   }
-  for (int j = threadIdx.x; j < d; j += COMBINE_THREADS) {
-    float v = s_row[j];
+  // every thread re-reads only the columns it wrote itself
+  for (int j = threadIdx.x * 4; j < d; j += COMBINE_THREADS * 4) {
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = s_row[j + i];
     if (add_residual) {
-      if (out_norm_w != nullptr) v = out_norm_w[j] * (v * scale);
-      v += load1<TH>(h + static_cast<size_t>(t) * d + j);
+      float r[4];
+      load4<TH>(h + t * d + j, r);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (out_norm_w != nullptr) v[i] = out_norm_w[j + i] * (v[i] * scale);
+        v[i] += r[i];
+      }
     }
-    store1<TY>(y + static_cast<size_t>(t) * d + j, v);
+    store4<TY>(y + t * d + j, v);
   }
 }
 
@@ -819,6 +1003,7 @@ int launch_combine(const void* dpart, int d_dtype, int ksplit, int pairs, const 
   const int d = L->hidden, k = L->top_k;
   const size_t smem = static_cast<size_t>(d) * sizeof(float);
   B200_REQUIRE(smem <= 48 * 1024, "combine: hidden (%d) too large", d);
+  B200_REQUIRE(d % 4 == 0 && k >= 1 && k <= MAX_TOPK, "combine: hidden must be a multiple of 4, top_k 1..8");
   const size_t stride = static_cast<size_t>(pairs) * d;
   const bool need_row = L->layer_output_norm_weight != nullptr && add_residual;
   int slices = 1;

@@ -238,7 +238,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
     for (int st = 0; st < args.stages_per_item; ++st, ++n) {
       const int slot = n % STAGES;
       const uint32_t phase = (n / STAGES) & 1u;
-      if (!mbar_wait(full_bar(slot), phase, abort_flag, args.status)) break;
+      if (!mbar_wait_warp(full_bar(slot), phase, abort_flag, args.status)) break;
       const uint32_t sb = smem_base + slot * C::STAGE;
 
       if constexpr (LAYOUT == B200MOE_LAYOUT_Q8_0) {
@@ -415,7 +415,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
           int col = tile * SET_ROWS + rsub;
           if (args.out_kperm) col = (col & ~7) | ((col & 3) << 1) | ((col >> 2) & 1);
           static_cast<__half*>(args.out)[static_cast<size_t>(tok) * args.N + col] =
-              to_half_sat(a * up);
+              to_half_sat(a * up, args.status);
         } else {
           float* outp = static_cast<float*>(args.out) +
                         static_cast<size_t>(kc) * args.P * args.N +

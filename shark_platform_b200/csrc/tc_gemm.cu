@@ -48,24 +48,37 @@ constexpr int TC_WARP_MMA = TC_DQ_WARPS + 2;
 constexpr int TC_THREADS = (TC_DQ_WARPS + 3) * 32;
 constexpr int TC_KT = 64;            // k per stage (one token slot, one A slot)
 constexpr int TC_ROWS = 128;         // weight rows per set
-constexpr int TC_NTOK = 192;         // token rows of the staged tile / accumulator columns
+constexpr int TC_NTOK = 192;         // largest token tile / accumulator width
 constexpr int TC_MAX_E = 64;
-constexpr int TC_WSLOTS = 2;
 constexpr int TC_WSET = TC_ROWS * 128;          // bytes of one set in a weight slot (128 k)
 constexpr int TC_WSLOT = 2 * TC_WSET;
-constexpr int TC_XSLOTS = 6;
-constexpr int TC_XSLOT = TC_NTOK * TC_KT * 2;
 constexpr int TC_SGROUP = 4;                    // stages covered by one scale tile (256 k)
 constexpr int TC_SSLOTS = 2;
 constexpr int TC_SSET = TC_ROWS * 32;           // per row and group: 8 fp16 scales (Q8_0, 16 B used) or 8 half2 scale/min pairs (Q4_K)
 constexpr int TC_SSLOT = 2 * TC_SSET;
-constexpr int TC_OFF_X = TC_WSLOTS * TC_WSLOT;
-constexpr int TC_OFF_S = TC_OFF_X + TC_XSLOTS * TC_XSLOT;
-constexpr int TC_OFF_BAR = TC_OFF_S + TC_SSLOTS * TC_SSLOT;
-constexpr int TC_SMEM = 1024 + TC_OFF_BAR + 256;
-constexpr uint32_t TC_COL_ACC0 = 0, TC_COL_ACC1 = 192, TC_COL_A = 384;
-static_assert(TC_WSLOT % 1024 == 0 && TC_XSLOT % 1024 == 0, "slot alignment for the swizzle");
-static_assert(TC_SMEM <= 232448, "shared memory budget");
+
+// Geometry for token tiles of at most NMAX rows.  The two accumulators take
+// 2 x NMAX tensor-memory columns; what is left of the 512 holds A staging slots
+// of 64 columns, so narrow tiles get a deeper A ring (the MMA lane and the
+// dequant warps then rarely wait for each other) and, because their token slots
+// are small, a deeper weight ring (more bytes in flight per SM, which is what a
+// weight-streaming tile needs).
+template <int NMAX>
+struct TcCfg {
+  static_assert(NMAX == 64 || NMAX == 128 || NMAX == 192, "token tile widths: 64, 128, 192");
+  static constexpr int ASLOTS = (512 - 2 * NMAX) / 64;  // 6, 4, 2 (even: a slot belongs to one dequant group)
+  static constexpr int WSLOTS = NMAX == 192 ? 2 : NMAX == 128 ? 3 : 5;
+  static constexpr int XSLOTS = 6;
+  static constexpr int XSLOT = NMAX * TC_KT * 2;
+  static constexpr int OFF_X = WSLOTS * TC_WSLOT;
+  static constexpr int OFF_S = OFF_X + XSLOTS * XSLOT;
+  static constexpr int OFF_BAR = OFF_S + TC_SSLOTS * TC_SSLOT;
+  static constexpr int SMEM = 1024 + OFF_BAR + 512;
+  static constexpr uint32_t COL_ACC0 = 0, COL_ACC1 = NMAX, COL_A = 2 * NMAX;
+  static_assert(XSLOT % 1024 == 0 && TC_WSLOT % 1024 == 0, "slot alignment for the swizzle");
+  static_assert(SMEM <= 232448, "shared memory budget");
+  static_assert(2 * (WSLOTS + XSLOTS + TC_SSLOTS + ASLOTS) + 2 <= 64, "barrier area");
+};
 
 struct TcArgs {
   const int32_t* seg;
@@ -171,7 +184,7 @@ __device__ __forceinline__ uint32_t make_idesc(int m, int n) {
   return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-template <int LAYOUT, int NMAT>
+template <int LAYOUT, int NMAT, int NMAX>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                const __grid_constant__ CUtensorMap tm_s0, const __grid_constant__ CUtensorMap tm_s1,
@@ -185,16 +198,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   __shared__ int s_abort;
   __shared__ uint32_t s_tmem;
 
+  using G = TcCfg<NMAX>;
+  constexpr int TC_WSLOTS = G::WSLOTS, TC_XSLOTS = G::XSLOTS, TC_XSLOT = G::XSLOT, TC_ASLOTS = G::ASLOTS;
+  constexpr uint32_t TC_COL_ACC0 = G::COL_ACC0, TC_COL_ACC1 = G::COL_ACC1, TC_COL_A = G::COL_A;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t x_base = smem_base + TC_OFF_X;
-  const uint32_t scale_base = smem_base + TC_OFF_S;
-  const uint32_t bar_base = smem_base + TC_OFF_BAR;
+  const uint32_t x_base = smem_base + G::OFF_X;
+  const uint32_t scale_base = smem_base + G::OFF_S;
+  const uint32_t bar_base = smem_base + G::OFF_BAR;
   int nb = 0;
   auto take = [&](int n) { const uint32_t b = bar_base + 8u * nb; nb += n; return b; };
   const uint32_t wfull = take(TC_WSLOTS), wempty = take(TC_WSLOTS);
   const uint32_t xfull = take(TC_XSLOTS), xempty = take(TC_XSLOTS);
   const uint32_t sfull = take(TC_SSLOTS), sempty = take(TC_SSLOTS);
-  const uint32_t a_ready = take(2), a_free = take(2);
+  const uint32_t a_ready = take(TC_ASLOTS), a_free = take(TC_ASLOTS);
   const uint32_t acc_full_bar = take(1), acc_empty_bar = take(1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -212,7 +228,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       mbar_init(sfull + 8u * s, 1);
       mbar_init(sempty + 8u * s, TC_DQ_WARPS);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < TC_ASLOTS; ++s) {
       mbar_init(a_ready + 8u * s, 256);
       mbar_init(a_free + 8u * s, 1);
     }
@@ -352,9 +368,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         tc_fence_after();
         for (int st = 0; st < stages_per_tile; ++st, ++n) {
           const int xs = n % TC_XSLOTS;
-          const int as = n & 1;
+          const int as = n % TC_ASLOTS;
           if (!mbar_wait(xfull + 8u * xs, (n / TC_XSLOTS) & 1u, abort_flag, args.status) ||
-              !mbar_wait(a_ready + 8u * as, (n >> 1) & 1u, abort_flag, args.status)) {
+              !mbar_wait(a_ready + 8u * as, (n / TC_ASLOTS) & 1u, abort_flag, args.status)) {
             ok = false;
             break;
           }
@@ -390,7 +406,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       for (int sg = 0; sg < stages_per_tile / TC_SGROUP && ok; ++sg) {
         const uint32_t g = n / TC_SGROUP;
         const int ss = g % TC_SSLOTS;
-        if (!mbar_wait(sfull + 8u * ss, (g / TC_SSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
+        if (!mbar_wait_warp(sfull + 8u * ss, (g / TC_SSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
         // Q8_0: 8 fp16 block scales of the 256-k group; Q4_K: 8 (scale, min) half2 pairs
         uint32_t scw[8];
         if constexpr (Q4) {
@@ -408,8 +424,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           // this group's half (64 k) of the weight slot
           const uint32_t wi = n >> 1;
           const int ws = wi % TC_WSLOTS;
-          const int as = n & 1;
-          if (!mbar_wait(wfull + 8u * ws, (wi / TC_WSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
+          const int as = n % TC_ASLOTS;  // even slot count: slot parity == this group's stage parity
+          if (!mbar_wait_warp(wfull + 8u * ws, (wi / TC_WSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
           uint32_t v[32];
           if constexpr (Q4) {
             // 64-byte rows (128 k of nibbles), 64-byte swizzle; this stage = chunks 2*grp, 2*grp+1
@@ -446,7 +462,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
               for (int j = 0; j < 4; ++j)
                 dequant_q8x4(q[c][j], c < 2 ? s_lo : s_hi, v[c * 8 + 2 * j], v[c * 8 + 2 * j + 1]);
           }
-          if (!mbar_wait(a_free + 8u * as, ((n >> 1) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          if (!mbar_wait_warp(a_free + 8u * as, ((n / TC_ASLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
           tc_fence_after();
           tmem_st32(tmem + lane_addr + TC_COL_A + as * 64 + set * 32, v);
           tmem_wait_st();
@@ -456,7 +472,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       }
       if (!ok) break;
       // ---- epilogue: each of the four warpgroups takes every fourth 16-token column chunk
-      if (!mbar_wait(acc_full_bar, ti & 1u, abort_flag, args.status)) break;
+      if (!mbar_wait_warp(acc_full_bar, ti & 1u, abort_flag, args.status)) break;
       tc_fence_after();
       const int seg_end = row0 + rows;
       for (int c0 = (grp * 2 + set) * 16; c0 < ncols; c0 += 64) {
@@ -473,7 +489,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
             const float a = args.act == B200MOE_ACT_SILU ? silu_f(gv) : gelu_erf_f(gv);
             int col = (nt & 0xffff) * TC_ROWS + row;
             if (args.out_kperm) col = (col & ~7) | ((col & 3) << 1) | ((col >> 2) & 1);
-            static_cast<__half*>(args.out)[static_cast<size_t>(tok) * args.N + col] = to_half_sat(a * uv);
+            static_cast<__half*>(args.out)[static_cast<size_t>(tok) * args.N + col] = to_half_sat(a * uv, args.status);
           } else {
             float* o = static_cast<float*>(args.out) +
                        static_cast<size_t>(nt >> 16) * args.P * args.N +
@@ -497,20 +513,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   }
 }
 
-template <int LAYOUT, int NMAT>
-int tc_launch(const CUtensorMap* maps, const TcArgs& a, cudaStream_t st) {
-  auto kern = tc_gemm_kernel<LAYOUT, NMAT>;
+template <int LAYOUT, int NMAT, int NMAX>
+int tc_launch_n(const CUtensorMap* maps, const TcArgs& a, cudaStream_t st) {
+  auto kern = tc_gemm_kernel<LAYOUT, NMAT, NMAX>;
+  using G = TcCfg<NMAX>;
   static bool configured[16] = {};
   int dev = 0;
   B200_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 16 && !configured[dev]) {
-    B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
+    B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM));
     configured[dev] = true;
   }
-  kern<<<sm_count(), TC_THREADS, TC_SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+  kern<<<sm_count(), TC_THREADS, G::SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
                                                 maps[6], maps[7], maps[8], maps[9], a);
   B200_CHECK_CUDA(cudaGetLastError());
   return B200MOE_OK;
+}
+
+// The kernel variant follows the token tile: <= 64, <= 128 or <= 192 rows.
+template <int LAYOUT, int NMAT>
+int tc_launch(const CUtensorMap* maps, const TcArgs& a, cudaStream_t st) {
+  if (a.tok_tile <= 64) return tc_launch_n<LAYOUT, NMAT, 64>(maps, a, st);
+  if (a.tok_tile <= 128) return tc_launch_n<LAYOUT, NMAT, 128>(maps, a, st);
+  return tc_launch_n<LAYOUT, NMAT, 192>(maps, a, st);
+}
+
+// Token tile for an expected number of rows per expert: experts with few rows
+// stream their weights through the narrow, deeply buffered variants.  A
+// segment longer than the tile simply takes several tiles.
+int tc_pick_tok_tile(int tok_tile, int pairs, int experts) {
+  const int est = pairs / (experts > 0 ? experts : 1);
+  if (est <= 40) return tok_tile < 64 ? tok_tile : 64;
+  if (est <= 96) return tok_tile < 128 ? tok_tile : 128;
+  return tok_tile;
 }
 
 // Token-tile tensor maps with box heights 16, 32, 64, 96, 128 and 192 (maps[4..9]).
@@ -549,8 +584,14 @@ int tc_weight_map(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts) {
 
 }  // namespace
 
-bool tc_supported(const b200moe_weight_t* w) {
-  return (w->layout == B200MOE_LAYOUT_Q8_0 || w->layout == B200MOE_LAYOUT_Q4_K) && w->cols % 256 == 0;
+// Every shape condition the launchers below check, so that the automatic regime
+// choice never picks the tensor kernel for a layer only the stream kernel can
+// tile.  `down` selects the down projection's row rule (two 128-row sets of
+// consecutive rows per tile) instead of the gate/up one (128 rows per set).
+bool tc_supported(const b200moe_weight_t* w, bool down) {
+  if (!(w->layout == B200MOE_LAYOUT_Q8_0 || w->layout == B200MOE_LAYOUT_Q4_K)) return false;
+  if (w->cols % 256 != 0 || w->experts < 1 || w->experts > TC_MAX_E) return false;
+  return w->rows % (down ? 2 * TC_ROWS : TC_ROWS) == 0;
 }
 
 int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_tile,
@@ -569,7 +610,7 @@ int launch_tc_gate_up(const void* xs, const int32_t* seg, int pairs, int tok_til
   if (int rc = tc_token_maps(maps, xs, pairs, static_cast<uint64_t>(gate->cols) * 2)) return rc;
   TcArgs a{};
   a.seg = seg; a.E = gate->experts; a.N = gate->rows; a.K = gate->cols;
-  a.ntiles = gate->rows / TC_ROWS; a.tok_tile = tok_tile; a.P = pairs; a.act = act;
+  a.ntiles = gate->rows / TC_ROWS; a.tok_tile = tc_pick_tok_tile(tok_tile, pairs, gate->experts); a.P = pairs; a.act = act;
   a.ksplit = 1;
   a.out_kperm = out_kperm;
   a.out = a_out; a.status = device_status_ptr();
@@ -620,7 +661,7 @@ int launch_tc_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile
   a.seg = seg; a.E = down->experts; a.N = down->rows; a.K = down->cols;
   B200_REQUIRE(ksplit >= 1 && (down->cols / TC_KT) % (4 * ksplit) == 0, "tensor kernel: bad k split %d",
                ksplit);
-  a.ntiles = down->rows / (2 * TC_ROWS); a.tok_tile = tok_tile; a.P = pairs; a.act = 0;
+  a.ntiles = down->rows / (2 * TC_ROWS); a.tok_tile = tc_pick_tok_tile(tok_tile, pairs, down->experts); a.P = pairs; a.act = 0;
   a.ksplit = ksplit;
   a.out = d_out; a.status = device_status_ptr();
   a.total_rows = static_cast<long long>(down->experts) * down->rows;

@@ -29,7 +29,8 @@ from . import _cabi as C
 from . import ops as _ops
 
 _DT = {torch.float32: C.DT_F32, torch.float16: C.DT_F16, torch.bfloat16: C.DT_BF16}
-REGIMES = {"auto": C.REGIME_AUTO, "stream": C.REGIME_STREAM, "tensor": C.REGIME_TENSOR}
+REGIMES = {"auto": C.REGIME_AUTO, "stream": C.REGIME_STREAM, "tensor": C.REGIME_TENSOR,
+           "tensor_pair": C.REGIME_TENSOR_PAIR}
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -194,7 +195,9 @@ def route_plan(experts: torch.Tensor, expert_count: int, expert_begin: int = 0) 
     dev = ex.device
     counts = torch.empty(expert_count, dtype=torch.int32, device=dev)
     seg = torch.empty(expert_count + 1, dtype=torch.int32, device=dev)
-    perm = torch.empty(max(pairs, 1), dtype=torch.int32, device=dev)
+    # zero-filled: with an expert range that drops pairs, positions past the last
+    # kept pair are not written and must still be valid row numbers
+    perm = torch.zeros(max(pairs, 1), dtype=torch.int32, device=dev)
     inv = torch.empty(max(pairs, 1), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         C.check(C.lib.b200moe_route_plan(_ptr(ex), pairs, expert_begin, expert_count, _ptr(counts),
@@ -346,32 +349,58 @@ class B200MoeStack(torch.nn.Module):
 class GatheredExperts:
     """What `ffn_*_exps.weight[experts, :, :]` returns for a quantized tensor: a
     handle on (weights, experts) with the logical shape [T, k, N, K] of the dense
-    gather the reference would have materialised (layers/ffn_moe_block.py:39)."""
+    gather the reference would have materialised (layers/ffn_moe_block.py:39).
+    For one shard of an expert-sharded tensor, `expert_begin` is the global id of
+    the shard's first expert; pairs routed elsewhere contribute zero rows."""
+
+    def __init__(self, base, experts: torch.Tensor, expert_begin: int = 0):
+        self.base = base
+        self.experts = experts
+        self.expert_begin = expert_begin
+        t, k = experts.shape
+        self.shape = [t, k, int(base.shape[1]), int(base.shape[2])]
+
+    def plan(self, device) -> RoutePlan:
+        return _cached_plan(self.experts, int(self.base.shape[0]), self.expert_begin, device)
+
+
+def _cached_plan(experts: torch.Tensor, expert_count: int, expert_begin: int = 0,
+                 device=None) -> RoutePlan:
+    """One route plan per `experts` tensor OBJECT (and expert range), kept on the
+    tensor itself.
+
+    PreGatherFFNMOE.forward indexes all three expert tensors with the same
+    `experts` object (layers/ffn_moe_block.py:60-74), so the plan built for the
+    gate product is found again for up and down.  The plan dies with the tensor.
+    Nothing is keyed on the address: the next layer's (or decode step's)
+    `torch.topk` result has the same shape, version 0 and, from the caching
+    allocator, very often the same address as the one just freed."""
+    device = experts.device if device is None else torch.device(device)
+    plans = getattr(experts, "_b200moe_plans", None)
+    if plans is None or plans.get("version") != experts._version:
+        plans = {"version": experts._version}
+        experts._b200moe_plans = plans
+    key = (expert_begin, expert_count, str(device))
+    if key not in plans:
+        plans[key] = route_plan(experts.to(device), expert_count, expert_begin)
+    return plans[key]
+
+
+class ShardedGatheredExperts:
+    """`weights[experts, :, :]` on an expert-sharded `SplitPrimitiveTensor`
+    (shard_dim 0, shards = quantized tensors; types/tensors.py:957-1096): one
+    GatheredExperts per shard, each knowing its first global expert id."""
 
     def __init__(self, base, experts: torch.Tensor):
         self.base = base
         self.experts = experts
+        self.parts = []
+        begin = 0
+        for shard in base.shards:
+            self.parts.append(GatheredExperts(shard, experts, begin))
+            begin += int(shard.shape[0])
         t, k = experts.shape
         self.shape = [t, k, int(base.shape[1]), int(base.shape[2])]
-        self._plan: Optional[RoutePlan] = None
-
-    def plan(self) -> RoutePlan:
-        if self._plan is None:
-            self._plan = _cached_plan(self.experts, int(self.base.shape[0]))
-        return self._plan
-
-
-_PLAN_CACHE: dict = {}
-
-
-def _cached_plan(experts: torch.Tensor, expert_count: int) -> RoutePlan:
-    key = (experts.data_ptr(), experts._version, tuple(experts.shape), expert_count)
-    hit = _PLAN_CACHE.get("key")
-    if hit == key:
-        return _PLAN_CACHE["plan"]
-    plan = route_plan(experts, expert_count)
-    _PLAN_CACHE["key"], _PLAN_CACHE["plan"] = key, plan
-    return plan
 
 
 _SUPPORTED = ("BlockScaledLayout", "SuperBlockOffsetScaled_4_6_Layout")
@@ -392,22 +421,20 @@ def get_index_quantized(tensor, key):
     return GatheredExperts(tensor, idx)
 
 
-def einsum_2args_gathered(input0, input1, einsum_str):
-    """`einsum_2args` override for the MoE strings with a GatheredExperts rhs
-    (ops/default_impls.py:72-94): "mk,menk->men" and "mek,menk->men"."""
-    if not isinstance(input1, GatheredExperts):
-        return NotImplemented
-    x = _unbox(input0)
-    if not x.is_cuda:
-        return NotImplemented
-    plan = input1.plan()
-    w = prepare_weight(input1.base)
-    t, k = input1.experts.shape
+def _gathered_product(x: torch.Tensor, g: GatheredExperts, einsum_str: str):
+    """[T, k, N] fp32 on the weights' device: rows of pairs whose expert lies in
+    g's expert range, zeros elsewhere.  None for an einsum string that is not one
+    of the two MoE products."""
+    w = prepare_weight(g.base)
+    dev = w.keep[0].device
+    plan = g.plan(dev)
+    t, k = g.experts.shape
+    x = x.to(dev)
     kperm = C.lib.b200moe_kperm(w.layout, C.REGIME_AUTO, t)
     if einsum_str == "mk,menk->men":
         rows = x.to(torch.float16).contiguous()
-        xs = torch.empty(plan.pairs, w.cols, dtype=torch.float16, device=x.device)
-        with torch.cuda.device(x.device):
+        xs = torch.empty(plan.pairs, w.cols, dtype=torch.float16, device=dev)
+        with torch.cuda.device(dev):
             C.check(C.lib.b200moe_permute_rows(_ptr(rows), _ptr(plan.perm), _ptr(plan.seg_offsets),
                                                w.experts, plan.pairs, k, w.cols, kperm, _ptr(xs),
                                                _stream()), "permute_rows")
@@ -417,9 +444,84 @@ def einsum_2args_gathered(input0, input1, einsum_str):
         if kperm:
             xs = xs.view(plan.pairs, -1, 2, 4).transpose(2, 3).reshape(plan.pairs, -1).contiguous()
     else:
-        return NotImplemented
+        return None
     out = grouped_matmul(xs, plan.seg_offsets, w, t)
-    return out.index_select(0, plan.inv.to(torch.int64)).view(t, k, w.rows).to(x.dtype)
+    inv = plan.inv.to(torch.int64)
+    res = out.index_select(0, inv.clamp_min(0))
+    if g.expert_begin != 0 or w.experts != _total_experts(g):
+        res = res * (inv >= 0).unsqueeze(1)  # rows past the kept pairs were never computed
+    return res.view(t, k, w.rows)
+
+
+def _total_experts(g: GatheredExperts) -> int:
+    return getattr(g, "total_experts", int(g.base.shape[0]))
+
+
+def einsum_2args_gathered(input0, input1, einsum_str):
+    """`einsum_2args` override for the MoE strings with a GatheredExperts rhs
+    (ops/default_impls.py:72-94): "mk,menk->men" and "mek,menk->men"."""
+    if not isinstance(input1, GatheredExperts):
+        return NotImplemented
+    x = _unbox(input0)
+    if not x.is_cuda:
+        return NotImplemented
+    res = _gathered_product(x, input1, einsum_str)
+    if res is None:
+        return NotImplemented
+    return res.to(device=x.device, dtype=x.dtype)
+
+
+def get_index_split(tensor, key):
+    """`get_index` override for an expert-sharded `SplitPrimitiveTensor` whose
+    shards are Q8_0 / Q4_K planar tensors (the reference has no sharded
+    get_index at all, ops/sharded_impls.py)."""
+    shards = getattr(tensor, "shards", None)
+    if not shards or getattr(tensor, "shard_dim", None) != 0:
+        return NotImplemented
+    if any(_layout_name(sh) not in _SUPPORTED for sh in shards):
+        return NotImplemented
+    if not (isinstance(key, tuple) and len(key) == 3 and isinstance(key[0], torch.Tensor)):
+        return NotImplemented
+    idx = key[0]
+    if idx.dtype not in (torch.int64, torch.int32) or idx.dim() != 2 or not idx.is_cuda:
+        return NotImplemented
+    if key[1] != slice(None) or key[2] != slice(None):
+        return NotImplemented
+    return ShardedGatheredExperts(tensor, idx)
+
+
+def einsum_2args_sharded_gathered(input0, input1, einsum_str):
+    """The two MoE products against an expert-sharded weight: every shard
+    multiplies, on its own device, the pairs routed to its experts; the disjoint
+    partial results are added on the device of the activations.  `input0` is a
+    plain tensor (result: a plain tensor on its device) or a `ReplicatedTensor`
+    (shard i feeds weight shard i; result: replicated again).  One process
+    holding all shards, as in the reference's sharding model
+    (types/tensors.py:743-955); with one process per GPU use
+    `parallel.build_block` instead, which exchanges tokens rather than results."""
+    if not isinstance(input1, ShardedGatheredExperts):
+        return NotImplemented
+    rep = getattr(input0, "shards", None)
+    if rep is not None and getattr(input0, "shard_dim", None) is not None:
+        return NotImplemented  # split activations are not a replicated operand
+    xs = [_unbox(sh) for sh in rep] if rep is not None else None
+    x0 = xs[0] if xs is not None else _unbox(input0)
+    if not x0.is_cuda:
+        return NotImplemented
+    total = None
+    n_parts = len(input1.parts)
+    for i, part in enumerate(input1.parts):
+        part.total_experts = int(input1.base.shape[0])
+        xi = xs[i] if xs is not None and len(xs) == n_parts else x0
+        res = _gathered_product(xi, part, einsum_str)
+        if res is None:
+            return NotImplemented
+        res = res.to(x0.device)
+        total = res if total is None else total + res
+    total = total.to(x0.dtype)
+    if rep is None:
+        return total
+    return type(input0)(ts=[total.to(x.device) for x in xs])
 
 
 def einsum_2args_gate_scale(input0, input1, einsum_str):
@@ -478,15 +580,23 @@ def linear_quantized(input, weight, bias=None, *, accum_dtype=None):
     return y
 
 
-def register_overrides(ops_module=_ops, quantized_type=None, tensor_type=torch.Tensor, salience=10):
+def register_overrides(ops_module=_ops, quantized_type=None, tensor_type=torch.Tensor, salience=10,
+                       split_type=None, replicated_type=None):
     """Registers the overrides with an ops registry: this package's mirror by
     default, sharktank's own when called from `plugin.register`."""
     from . import types as _types
 
     qt = quantized_type or _types.QuantizedTensor
+    split = split_type or _types.SplitPrimitiveTensor
+    repl = replicated_type or _types.ReplicatedTensor
     ops_module.get_index.override(qt, salience=salience)(get_index_quantized)
+    ops_module.get_index.override(split, salience=salience)(get_index_split)
     ops_module.einsum_2args.override(tensor_type, GatheredExperts, salience=salience)(
         einsum_2args_gathered)
+    ops_module.einsum_2args.override(tensor_type, ShardedGatheredExperts, salience=salience)(
+        einsum_2args_sharded_gathered)
+    ops_module.einsum_2args.override(repl, ShardedGatheredExperts, salience=salience)(
+        einsum_2args_sharded_gathered)
     ops_module.matmul.override(tensor_type, qt, salience=salience)(matmul_quantized)
     if ops_module is _ops:
         ops_module.linear.override(tensor_type, qt, salience=salience)(linear_quantized)

@@ -12,8 +12,11 @@ these are consulted first; sharktank/ops/_registry.py:211-244):
   only implements this for Q4_1, ops/default_impls.py:204-218);
 * `einsum_2args(Tensor, GatheredExperts, str)` — the MoE einsums of
   `PreGatherFFNMOE` as grouped products on the GPU;
-* the same pair for expert-sharded weights (`SplitPrimitiveTensor` whose shards
-  are quantized tensors) with replicated activations.
+* the same pair for expert-sharded weights: `get_index(SplitPrimitiveTensor,
+  key)` (shard_dim 0, shards = quantized tensors) and `einsum_2args(Tensor |
+  ReplicatedTensor, ShardedGatheredExperts, str)` — each shard multiplies the
+  pairs routed to its experts on its own device and the disjoint partial results
+  are added (one process holding all shards, the reference's sharding model).
 
 Both overrides decline (`NotImplemented`) for CPU tensors and other layouts, so
 the reference's own dispatch continues unchanged for everything else.
@@ -33,10 +36,22 @@ def register(salience: int = 10):
     if _registered:
         return
     import sharktank.ops as st_ops
-    from sharktank.types import QuantizedTensor
+    from sharktank.types import QuantizedTensor, ReplicatedTensor, SplitPrimitiveTensor
 
     moe.register_overrides(st_ops, quantized_type=QuantizedTensor, tensor_type=torch.Tensor,
-                           salience=salience)
+                           salience=salience, split_type=SplitPrimitiveTensor,
+                           replicated_type=ReplicatedTensor)
+    # SplitPrimitiveTensor has its own __getitem__ (types/tensors.py:1056-1080)
+    # that never consults the registry and refuses any key on the split
+    # dimension, so `weights[experts, :, :]` on expert-sharded weights cannot
+    # reach the override above.  Ask the override first, fall through otherwise.
+    reference_getitem = SplitPrimitiveTensor.__getitem__
+
+    def getitem(self, key):
+        result = moe.get_index_split(self, key)
+        return reference_getitem(self, key) if result is NotImplemented else result
+
+    SplitPrimitiveTensor.__getitem__ = getitem
     _registered = True
 
 

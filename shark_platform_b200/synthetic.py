@@ -221,30 +221,61 @@ def case_input(case: Case, device="cuda") -> torch.Tensor:
 
 
 def make_case_on_device(spec: CaseSpec, device="cuda", seed: Optional[int] = None) -> Case:
-    """Same distributions as `make_case`, drawn with the device generator.  For
-    benchmarks that need tens of gigabytes of distinct weights (the 32-layer
-    stack); values differ from the CPU-seeded case of the same seed."""
+    """Same distributions as `make_case` for layers too large to draw on the
+    host (tens of gigabytes for the 32-layer stack, a minute per Mixtral layer):
+    the expert planes come from the device generator, the small tensors
+    (activations, router, bias) from the seeded CPU generator, so the routing of
+    a seed is reproducible on any machine.  The expert values differ from the
+    CPU-seeded case of the same seed."""
     T, d, f, e = spec.tokens, spec.hidden, spec.ffn, spec.experts
-    gen = torch.Generator(device=device).manual_seed(spec.seed if seed is None else seed)
-    rn = lambda *shape: torch.randn(*shape, generator=gen, device=device)
-    h = rn(1, T, d)
+    sd = spec.seed if seed is None else seed
+    cpu_gen = torch.Generator(device="cpu").manual_seed(sd)
+    h = torch.randn(1, T, d, generator=cpu_gen)
     if spec.act_dtype == "bf16":
         h = h.to(torch.bfloat16).to(torch.float32)
-    router_w = rn(e, d) * 0.02
+    router_w = torch.randn(e, d, generator=cpu_gen) * 0.02
     router_b = None
     if spec.router_bias == "zipf":
-        rank = torch.randperm(e, generator=gen, device=device) + 1
-        router_b = -1.2 * torch.log(rank.to(torch.float32))
+        router_b = zipf_bias(cpu_gen, e)
     elif spec.router_bias == "normal":
-        router_b = rn(e) * 0.5
+        router_b = torch.randn(e, generator=cpu_gen) * 0.5
+    h, router_w = h.to(device), router_w.to(device)
+    router_b = None if router_b is None else router_b.to(device)
     norm_w = torch.ones(d, device=device)
     out_norm_w = torch.ones(d, device=device) if spec.out_norm else None
-    if spec.kind != Q8_0:
-        raise NotImplementedError("device-side generation is implemented for Q8_0 only")
+    gen = torch.Generator(device=device).manual_seed(sd)
+    rn = lambda *shape: torch.randn(*shape, generator=gen, device=device)
 
-    def planes(n, k):
+    def q8(n, k):
         qs = torch.randint(-127, 128, (e, n, k // 32, 32), generator=gen, device=device, dtype=torch.int8)
         dd = (rn(e, n, k // 32, 1).abs() * 0.002).to(torch.float16)
         return {"d": dd, "qs": qs}
 
+    def q4k(n, k):
+        sup = k // 256
+        u8 = lambda hi, *shape: torch.randint(0, hi, shape, generator=gen, device=device, dtype=torch.uint8)
+
+        def six_bit():
+            v = u8(64, e, n, sup, 8)
+            lo, hi = v & 0xF, v >> 4
+            low = lo[..., 0::2] | (lo[..., 1::2] << 4)
+            high = hi[..., 0::4] | (hi[..., 1::4] << 2) | (hi[..., 2::4] << 4) | (hi[..., 3::4] << 6)
+            return high.contiguous(), low.contiguous()
+
+        sc_hi, sc_lo = six_bit()
+        mn_hi, mn_lo = six_bit()
+        return {
+            "d": (rn(e, n, sup, 1).abs() * 2.5e-4).to(torch.float16),
+            "dmin": (rn(e, n, sup, 1).abs() * 2.0e-3).to(torch.float16),
+            "sb_scales_high": sc_hi, "sb_scales_low": sc_lo,
+            "sb_mins_high": mn_hi, "sb_mins_low": mn_lo,
+            "qs": u8(256, e, n, sup, 8, 16),
+        }
+
+    if spec.kind == Q8_0:
+        planes = q8
+    elif spec.kind == Q4_K:
+        planes = q4k
+    else:
+        raise NotImplementedError("device-side generation covers the quantized layouts")
     return Case(spec, h, norm_w, router_w, router_b, out_norm_w, planes(f, d), planes(f, d), planes(d, f))

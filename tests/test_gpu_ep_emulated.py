@@ -80,3 +80,47 @@ def test_dispatch_and_return_round_trip(world, E, k, tokens):
         assert torch.equal(ret[r][:tokens * k, 0].float().cpu(), want)
         assert torch.equal(ret[r][:tokens * k, -1].float().cpu(), want)
         assert torch.equal(ret[r][:tokens * k, 1].float().cpu(), torch.full_like(want, 2.0 * r))
+
+
+def test_barrier_gives_up_when_a_peer_never_arrives():
+    """A lost rank: a world-2 descriptor whose second rank never signals.  The
+    barrier's bounded spin runs out (limit shortened to ~50 us for the test), the
+    kernel returns, the status word reports the timeout once, and the library
+    keeps working afterwards.  Nothing faults or hangs: the wait simply ends."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from shark_platform_b200 import _cabi as C, moe, synthetic as syn
+
+    assert moe.device_status() == 0
+    world, el = 2, 4
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    counts_all = [torch.zeros(world, world * el, dtype=torch.int32, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
+    rows = [torch.zeros(8, 64, dtype=torch.float16, device="cuda") for _ in range(world)]
+    ep = C.EpDesc()
+    ep.world, ep.rank, ep.experts_local = world, 0, el
+    for i in range(world):
+        ep.counts_all[i], ep.flags[i] = counts_all[i].data_ptr(), flags[i].data_ptr()
+        ep.recv_x[i], ep.ret_y[i] = rows[i].data_ptr(), rows[i].data_ptr()
+    seg2 = torch.full((el + 1,), -1, dtype=torch.int32, device="cuda")
+    C.check(C.lib.b200moe_set_wait_limit(100_000))
+    try:
+        C.check(C.lib.b200moe_ep_barrier(ctypes.byref(ep), 1, ctypes.c_void_p(seg2.data_ptr()), st))
+        torch.cuda.synchronize()  # the kernel came back
+    finally:
+        C.check(C.lib.b200moe_set_wait_limit(0))
+    assert flags[1].cpu().tolist() == [1, 0]   # rank 0 signalled its peer
+    assert flags[0].cpu().tolist() == [1, 0]   # and itself; the peer's flag never came
+    word = ctypes.c_int32(0)
+    rc = C.lib.b200moe_device_status(st, ctypes.byref(word))
+    assert rc == -4 and word.value & 1, (rc, word.value)       # B200MOE_ERR_DEVICE, wait timed out
+    assert "timed out" in C.last_error()
+    with pytest.raises(C.B200MoeError):
+        C.check(rc, "device_status")
+    assert moe.device_status() == 0                             # cleared by the read
+    # the library is still usable: an ordinary layer call, checked for a clean status
+    case = syn.make_case(syn.CASES["small_q8"])
+    blk = syn.case_block(case)
+    y = blk(syn.case_input(case))
+    assert torch.isfinite(y.float()).all()
+    assert moe.device_status() == 0

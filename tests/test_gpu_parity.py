@@ -225,6 +225,88 @@ def test_pregather_ops_path(M, name):
     assert orc.rel_l2(out.cpu(), want) < REL_L2_TOL
 
 
+def _pregather_forward(ops, theta, x, ex, gt):
+    """The body of PreGatherFFNMOE.forward (layers/ffn_moe_block.py:60-74)."""
+    silu = torch.nn.functional.silu
+    ffn_gate = ops.elementwise(silu, ops.einsum_2args(x, theta.tensor("ffn_gate_exps", "weight")[ex, :, :],
+                                                      "mk,menk->men"))
+    ffn_up = ops.einsum_2args(x, theta.tensor("ffn_up_exps", "weight")[ex, :, :], "mk,menk->men")
+    down = ops.einsum_2args(ffn_gate * ffn_up, theta.tensor("ffn_down_exps", "weight")[ex, :, :],
+                            "mek,menk->men")
+    return torch.sum(ops.einsum_2args(gt, down, "me,men->men"), dim=1)
+
+
+def test_pregather_ops_path_fresh_routing_each_call(M):
+    """Consecutive layers / decode steps: each call brings a NEW index tensor of
+    the same shape, and the allocator hands the freed address back.  The route
+    plan must follow the tensor object, never its address."""
+    from shark_platform_b200 import ops
+
+    case = syn.make_case(syn.CASES["small_q8"])
+    p = oracle_params(case)
+    theta = mirror_theta(case)
+    xn = orc.rms_norm(case.h, p.norm_w, p.eps).view(-1, case.spec.hidden)
+    gate, idx, _ = orc.router(xn, p.router_w, p.router_b, p.top_k)
+    x, gt = xn.cuda(), gate.cuda()
+    gen = torch.Generator().manual_seed(4)
+    routings = [idx] + [torch.stack([torch.randperm(8, generator=gen)[:2] for _ in range(idx.shape[0])])
+                        for _ in range(3)]
+    addresses = set()
+    for r in routings:
+        want = orc.experts_pregather(xn, r, gate, p.w_gate, p.w_up, p.w_down, torch.nn.functional.silu)
+        ex = r.cuda()
+        addresses.add(ex.data_ptr())
+        out = _pregather_forward(ops, theta, x, ex, gt)
+        assert orc.rel_l2(out.cpu(), want) < REL_L2_TOL
+        del ex, out
+    # not asserted (allocator behaviour), but this is the situation the test is about
+    print("distinct index-tensor addresses over 4 calls:", len(addresses))
+    assert M.device_status() == 0
+
+
+@pytest.mark.parametrize("name,split", [("small_q8", [4, 4]), ("small_q4k", [2, 6]), ("small_q8", [1, 1, 6])])
+def test_pregather_ops_path_on_expert_sharded_weights(M, name, split):
+    """`SplitPrimitiveTensor(ts=[PlanarQuantizedTensor...], shard_dim=0)` expert
+    weights (types/tensors.py:957-1096) with plain and with replicated
+    activations: every shard multiplies the pairs routed to its experts."""
+    from shark_platform_b200 import ops, types as T
+
+    case = syn.make_case(syn.CASES[name])
+    p = oracle_params(case)
+    xn = orc.rms_norm(case.h, p.norm_w, p.eps).view(-1, case.spec.hidden)
+    gate, idx, _ = orc.router(xn, p.router_w, p.router_b, p.top_k)
+    want = orc.experts_pregather(xn, idx, gate, p.w_gate, p.w_up, p.w_down, torch.nn.functional.silu)
+    whole = mirror_theta(case)
+
+    def shard(key):
+        full = whole.tensor(key, "weight")
+        planes = full.unpack().planes
+        parts, e0 = [], 0
+        for n in split:
+            sub = {k: v[e0:e0 + n].contiguous() for k, v in planes.items()}
+            shape = [n] + [int(v) for v in full.shape[1:]]
+            parts.append(T.PlanarQuantizedTensor(shape=shape, layout=type(full.unpack())(shape, **sub)))
+            e0 += n
+        return T.SplitPrimitiveTensor(ts=parts, shard_dim=0)
+
+    theta = T.Theta({k: {"weight": shard(k)} for k in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps")})
+    x, ex, gt = xn.cuda(), idx.cuda(), gate.cuda()
+    ops._test_enable_last_op_dispatch(True)
+    g = theta.tensor("ffn_gate_exps", "weight")[ex, :, :]
+    assert ops._test_get_last_op_dispatch() is M.get_index_split
+    assert isinstance(g, M.ShardedGatheredExperts) and len(g.parts) == len(split)
+    ops._test_enable_last_op_dispatch(False)
+    out = _pregather_forward(ops, theta, x, ex, gt)
+    assert orc.rel_l2(out.cpu(), want) < REL_L2_TOL
+    # replicated activations: the result comes back replicated
+    xr = T.ReplicatedTensor(ts=[x] * len(split))
+    up = ops.einsum_2args(xr, theta.tensor("ffn_up_exps", "weight")[ex, :, :], "mk,menk->men")
+    assert isinstance(up, T.ReplicatedTensor) and len(up.shards) == len(split)
+    want_up = torch.einsum("mk,menk->men", xn, p.w_up[idx].float())
+    assert orc.rel_l2(up.shards[-1].cpu(), want_up) < 5e-3
+    assert M.device_status() == 0
+
+
 def test_ops_decline_unsupported():
     from shark_platform_b200 import ops
     from shark_platform_b200 import types as T

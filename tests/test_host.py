@@ -7,6 +7,8 @@ import sys
 import pytest
 import torch
 
+from helpers import import_sharktank, reference_path
+
 
 @pytest.fixture(scope="module", autouse=True)
 def built_library():
@@ -96,16 +98,9 @@ def test_product_never_imports_the_oracle():
                 assert "oracle" not in text.replace("# oracle", ""), f"{f} mentions the oracle"
 
 
-REF = os.environ.get("SHARKTANK_SRC", os.path.join(os.sep, "root", "reference", "sharktank"))
-
-
-@pytest.mark.skipif(not os.path.isdir(REF), reason="sharktank checkout not present")
+@pytest.mark.skipif(reference_path() is None, reason="sharktank not available ($SHARKTANK_SRC or baseline/_ref)")
 def test_plugin_registers_ahead_of_sharktank_overrides():
-    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
-    sys.path.insert(0, REF)
-    import iree_stub
-
-    iree_stub.install()
+    import_sharktank()
     import sharktank.ops as st_ops
     from sharktank.types import PlanarQuantizedTensor
     from sharktank.types.layouts import BlockScaledLayout

@@ -121,3 +121,34 @@ def test_route_plan_definition():
     assert seg.tolist() == [0, 1, 4, 5, 8, 8]
     assert perm.tolist() == [3, 1, 2, 6, 5, 0, 4, 7]
     assert inv[perm].tolist() == list(range(8))
+
+
+# ---- the multi-threaded torch restatements used for full-size layers --------
+@pytest.mark.parametrize("kind", [syn.Q8_0, syn.Q4_K])
+def test_torch_dequant_equals_the_pinned_numpy_dequant(kind):
+    gen = torch.Generator().manual_seed(21)
+    mk = syn.q8_0_planes if kind == syn.Q8_0 else syn.q4_k_planes
+    planes = mk(gen, 3, 24, 1024)
+    want = orc.dequant(kind, {k: v.numpy() for k, v in planes.items()})
+    got = orc.dequant_torch(kind, planes).numpy()
+    assert got.shape == want.shape
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    g = load_golden("formats.npz")  # and on the reference-made fixture planes
+    if kind == syn.Q8_0:
+        t = orc.q8_0_dequant_torch({"d": torch.from_numpy(g["q8_d"]), "qs": torch.from_numpy(g["q8_qs"])})
+        assert np.array_equal(t.numpy().view(np.uint16), g["q8_dequant_f16"].view(np.uint16))
+    else:
+        names = ("d", "dmin", "sb_scales_high", "sb_scales_low", "sb_mins_high", "sb_mins_low", "qs")
+        t = orc.q4_k_dequant_torch({n: torch.from_numpy(np.ascontiguousarray(g["q4k_" + n])) for n in names})
+        assert np.array_equal(t.numpy().view(np.uint16), g["q4k_dequant_f16"].view(np.uint16))
+
+
+@pytest.mark.parametrize("name", ["small_q8", "small_grok", "small_top4"])
+def test_sampled_streamed_evaluation_equals_the_full_one(name):
+    case = syn.make_case(syn.CASES[name])
+    p = oracle_params(case)
+    want, mid = orc.moe_block(case.h, p, form="pregather")
+    sel = torch.tensor([0, 3, 4, case.spec.tokens - 1])
+    got, mid2 = orc.moe_block_sampled(case.h, p, lambda e: (p.w_gate[e], p.w_up[e], p.w_down[e]), sel)
+    assert torch.equal(mid2["experts"], mid["experts"])
+    assert orc.rel_l2(got, want.view(-1, case.spec.hidden)[sel]) < 1e-6
