@@ -3,29 +3,39 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 One "step" is one MoE-layer forward over one batch of synthetic tokens.  Prints
-ONE JSON line (rank 0).  Workloads (all hidden 4096, ffn 14336, 8 experts,
-top-2, SiLU, Q8_0 weights, bf16 activations, seeded synthetic values):
-  prefill4096  4096 tokens (default; tensor-core bound)
+ONE JSON line (rank 0).  Workloads (hidden 4096, ffn 14336, 8 experts, top-2,
+SiLU, Q8_0 weights, bf16 activations, seeded synthetic values unless noted):
+  prefill4096  4096 tokens (default; tensor-core bound).  On one GPU the line
+               also carries `secondary.decode32`: the 32-token decode workload
+               measured on the same layer in the same run
   decode32     32 tokens   (HBM bound: the weights are streamed once per call)
   decode1 / decode128
   q4k_decode32 / q4k_prefill2048   the same layer with Q4_K expert weights
   grok_prefill8192                 Grok-1 shape (hidden 6144, ffn 32768, GELU, output norm)
   stack32_decode64                 32 Mixtral layers back to back, 64 tokens, Zipf(1.2)
                                    router bias per layer (weights drawn on the device)
+  profile_small                    the Mixtral layer with a quarter of the ffn rows (3584;
+                                   374 MB of Q8_0 weights, larger than L2) for profiler
+                                   captures: --tokens sets the token count, --regime the
+                                   kernel family, --kind Q4_K the other layout
 
 With N > 1 (torchrun, one process per GPU) the experts are partitioned over the
-ranks, each rank routes tokens/N tokens and the token rows move by NCCL
-all-to-all; the total token count stays fixed ("strong" scaling).
+ranks, each rank routes tokens/N tokens and the token rows move between GPUs;
+the total token count stays fixed ("strong" scaling).
 
-`--impl reference` times the CPU restatement of the reference's torch-eager
-layer (oracle/moe_oracle.py, the gather + batched-GEMV form sharktank runs) on
-the host cores, on a bounded token sample per step.
+`--impl reference` times the reference's own torch-eager layer on the host
+cores: sharktank's MoeBlock itself when the package is importable (from
+$SHARKTANK_SRC or baseline/_ref, through the iree stand-in of tests/golden),
+else the CPU restatement in oracle/moe_oracle.py, on dequantised weights, a
+bounded token sample per step.
 """
 from __future__ import annotations
 
 import argparse
 import ctypes
+import dataclasses
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -46,8 +56,11 @@ WORKLOADS = {
     "q4k_prefill2048": ("mixtral_q4k", 2048),
     "grok_prefill8192": ("grok_q8", 8192),
     "stack32_decode64": ("mixtral_q8", 64),
+    "profile_small": ("mixtral_q8", 256),
 }
 STAGES = ["router", "route_plan", "permute", "gate_up", "down", "combine"]
+SOAK_S = 0.6          # same load before the timed region, so that it runs at the settled clock
+CPU_CHUNK = 4         # tokens per call of the reference layer (its gather is 470 MB fp32 per token and matrix)
 
 
 def measured_peaks():
@@ -109,27 +122,99 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_reference_setup(case, sample_tokens):
-    """Host-side dequantised weights and the token sample for the CPU arm."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from helpers import oracle_params
+def workload_config(args, spec_name, spec, tokens, layers, world, transport):
+    """The `config` object; both arms print exactly this."""
+    return {"workload": args.workload,
+            "layer": f"{spec_name} MoE FFN ({spec.kind} experts, {spec.activation})"
+                     + (f", stack of {layers} layers, value = layer-tokens/s" if layers > 1 else ""),
+            "tokens": tokens, "hidden": spec.hidden, "ffn": spec.ffn,
+            "experts": spec.experts, "top_k": spec.top_k, "regime": args.regime,
+            "parallelism": "single GPU" if world == 1 else f"ep{world}, exchange: {transport}",
+            "l2": "expert weights (>= 0.8 GB per layer) exceed L2 (126 MB); no flush"}
 
-    t0 = time.time()
-    params = oracle_params(case)
-    h = case.h[:, :sample_tokens].contiguous()
-    return params, h, time.time() - t0
+
+# ------------------------------------------------------------------ CPU arm
+def reference_source():
+    for cand in (os.environ.get("SHARKTANK_SRC", ""), os.path.join(ROOT, "baseline", "_ref")):
+        if cand and os.path.isdir(os.path.join(cand, "sharktank")):
+            return cand
+    return None
 
 
-def time_cpu(params, h, steps, warmup, chunk=4):
-    from oracle import moe_oracle as orc
+class CpuLayer:
+    """The layer on the host cores with dequantised weights: sharktank's own
+    MoeBlock when it can be imported (kind "reference"), else the oracle's
+    restatement of it (kind "port").  Tokens go through in chunks of CPU_CHUNK:
+    the reference gathers a dense [tokens, k, N, K] copy of the expert weights."""
 
-    for _ in range(warmup):
-        orc.moe_block(h, params, form="pregather", chunk=chunk)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        orc.moe_block(h, params, form="pregather", chunk=chunk)
-    dt = time.perf_counter() - t0
-    return h.shape[1] * steps / dt, dt / steps
+    def __init__(self, case):
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        from helpers import oracle_params
+
+        import torch.nn.functional as F
+
+        self.spec = case.spec
+        params = oracle_params(case)  # dequantised the way the reference's unbox_tensor does (fp16)
+        self.kind = "port"
+        self.how = "oracle/moe_oracle.py restatement of sharktank's MoeBlock (gather + batched-GEMV form)"
+        src = reference_source()
+        if src is not None:
+            try:
+                for p in (os.path.join(ROOT, "tests", "golden"), src):
+                    if p not in sys.path:
+                        sys.path.insert(0, p)
+                import iree_stub
+
+                iree_stub.install()
+                from sharktank.layers.mixture_of_experts_block import MoeBlock
+                from sharktank.types import DefaultPrimitiveTensor, Theta
+
+                tree = {
+                    "ffn_gate_inp": {"weight": DefaultPrimitiveTensor(data=params.router_w)},
+                    "ffn_norm": {"weight": DefaultPrimitiveTensor(data=params.norm_w)},
+                    "ffn_gate_exps": {"weight": DefaultPrimitiveTensor(data=params.w_gate)},
+                    "ffn_up_exps": {"weight": DefaultPrimitiveTensor(data=params.w_up)},
+                    "ffn_down_exps": {"weight": DefaultPrimitiveTensor(data=params.w_down)},
+                }
+                if params.router_b is not None:
+                    tree["ffn_gate_inp"]["bias"] = DefaultPrimitiveTensor(data=params.router_b)
+                if params.out_norm_w is not None:
+                    tree["layer_output_norm"] = {"weight": DefaultPrimitiveTensor(data=params.out_norm_w)}
+                act = F.silu if self.spec.activation == "silu" else F.gelu
+                self.block = MoeBlock(Theta(tree), self.spec.experts, self.spec.top_k, self.spec.eps,
+                                      moe_activation=act)
+                self.kind = "reference"
+                self.how = (f"sharktank's own MoeBlock.forward (unmodified, from {os.path.relpath(src, ROOT)}; "
+                            "iree-turbine replaced by the import stand-in of tests/golden)")
+            except Exception as exc:  # fall back to the restatement, say why
+                self.how += f" [sharktank import failed: {type(exc).__name__}: {str(exc)[:80]}]"
+        if self.kind == "port":
+            from oracle import moe_oracle as orc
+
+            self.block = lambda h: orc.moe_block(h, params, form="pregather", chunk=CPU_CHUNK)[0]
+
+    def forward(self, h):
+        """h: [1, T, d] fp32."""
+        with torch.no_grad():
+            return torch.cat([self.block(h[:, t0:t0 + CPU_CHUNK]) for t0 in range(0, h.shape[1], CPU_CHUNK)], 1)
+
+    def time(self, h, steps, warmup):
+        for _ in range(warmup):
+            self.forward(h)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self.forward(h)
+        dt = time.perf_counter() - t0
+        return h.shape[1] * steps / dt, dt / steps
+
+
+def cpu_sample_tokens(tokens, steps):
+    """Tokens per step of the CPU arm: at least 256 tokens over the timed steps
+    (the reference is linear in tokens: it processes them in independent
+    chunks), at least 16 and at most 256 per step, never more than the workload."""
+    per = max(16, -(-256 // max(steps, 1)))
+    per = -(-per // CPU_CHUNK) * CPU_CHUNK
+    return max(1, min(tokens, per, 256))
 
 
 def run_reference(args, spec_name, tokens):
@@ -140,27 +225,165 @@ def run_reference(args, spec_name, tokens):
 
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    sample = min(tokens, 8)
     spec = syn.CASES[spec_name]
+    layers = 32 if args.workload == "stack32_decode64" else 1
+    steps, warmup = args.steps, args.warmup
+    sample = cpu_sample_tokens(tokens, steps)
+    t0 = time.time()
     case = syn.make_case(spec, tokens=sample)
-    params, h, _ = cpu_reference_setup(case, sample)
-    steps, warmup = min(args.steps, 8), min(args.warmup, 1)
-    tps, per_step = time_cpu(params, h, steps, warmup)
-    sample_txt = (f"{sample} tokens per step of the {tokens}-token workload, torch-eager gather + "
-                  f"batched-GEMV form on dequantised fp16->fp32 weights, {steps} steps")
+    cpu = CpuLayer(case)
+    setup_s = time.time() - t0
+    tps, per_step = cpu.time(case.h, steps, warmup)
+    sample_txt = (f"{sample} tokens per step ({CPU_CHUNK} per layer call) of the {tokens}-token workload, "
+                  f"{steps} timed steps = {sample * steps} tokens after {warmup} warm-up steps; {cpu.how}; "
+                  f"weights dequantised to fp16 as the reference's unbox_tensor does, fp32 activations; "
+                  f"one layer" + (" of the 32 (every layer costs the same)" if layers > 1 else "")
+                  + f"; set-up {setup_s:.0f} s outside the timed region")
+    world = args.gpus
     print(json.dumps({
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": tps, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": per_step * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": args.workload,
-                   "layer": f"{spec_name} MoE FFN ({spec.kind} experts, {spec.activation})",
-                   "tokens": tokens, "hidden": spec.hidden, "ffn": spec.ffn,
-                   "experts": spec.experts, "top_k": spec.top_k},
+        "config": workload_config(args, spec_name, spec, tokens, layers, world, args.ep),
+        "sample_tokens": sample,
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": sample_txt},
+                         "kind": cpu.kind, "sample": sample_txt},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
+
+
+# ----------------------------------------------------------- one GPU, one layer
+def event_ms(fn, steps):
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1)
+
+
+def soak(fn, seconds=SOAK_S):
+    """Runs the step for `seconds` of wall time; returns the number of steps."""
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
+        for _ in range(4):
+            fn()
+        torch.cuda.synchronize()
+        n += 4
+    return n
+
+
+def stage_times(C, fn, steps):
+    C.check(C.lib.b200moe_profile_enable(1))
+    for _ in range(steps):
+        fn()
+    torch.cuda.synchronize()
+    stage_ms = (ctypes.c_float * 6)()
+    calls = ctypes.c_int32(0)
+    C.check(C.lib.b200moe_profile_read(stage_ms, ctypes.byref(calls)))
+    C.check(C.lib.b200moe_profile_enable(0))
+    n = max(int(calls.value), 1)
+    return {name: stage_ms[i] / n for i, name in enumerate(STAGES)}
+
+
+def roofline_single(syn, spec, tokens, stage, peaks, experts_total=None):
+    E = experts_total or spec.experts
+    experts_active = min(E, tokens * spec.top_k)
+    if tokens >= 512:
+        gu_flops = tokens * spec.top_k * 2 * 2 * spec.ffn * spec.hidden
+        ach = gu_flops / (stage["gate_up"] * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"]
+        return {"bound": "tensor", "kernel": "gate_up", "achieved": ach, "peak": peak,
+                "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
+                "peak_source": peaks["source"] + " (cuBLAS bf16 burst)"}
+    gu_bytes = experts_active * 2 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
+    ach = gu_bytes / (stage["gate_up"] * 1e-3) / 1e9
+    peak = peaks["hbm_gbs"]
+    # traffic is not measured inside this run (an ncu capture of the same kernel
+    # on a 374 MB case is summarised under profiles/)
+    return {"bound": "hbm", "kernel": "gate_up", "achieved": ach, "peak": peak,
+            "unit": "GB/s", "frac": ach / peak, "traffic": None,
+            "algorithmic_bytes": gu_bytes, "peak_source": peaks["source"] + " (copy)"}
+
+
+def e2e_pipeline(C, moe, layer, h, steps, regime, depth):
+    """The same metric through the host-buffer entry points: every step copies
+    its input from pinned host memory and its output back; `depth` steps are in
+    flight (depth 1 = one step at a time)."""
+    tokens = h.shape[0]
+    dev = h.device
+    hp = [h.cpu().pin_memory() for _ in range(max(depth, 1))]
+    yp = [torch.empty_like(hp[0]).pin_memory() for _ in range(max(depth, 1))]
+    nbytes = hp[0].numel() * hp[0].element_size()
+    pipe = moe.HostPipeline(layer, tokens, h.dtype, depth=depth, regime=regime)
+    for i in range(3):
+        pipe.submit(hp[i % depth], yp[i % depth])
+    pipe.drain()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        pipe.submit(hp[i % depth], yp[i % depth])
+    pipe.drain()
+    dt = time.perf_counter() - t0
+    y_last = yp[(steps - 1) % depth].to(dev)
+    pipe.close()
+    return {"value": tokens * steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": nbytes,
+            "d2h_bytes_per_step": nbytes, "steps_in_flight": depth}, y_last
+
+
+def measure_layer(C, moe, syn, block, h, spec, args, peaks, sampler=None, cold=True):
+    """value / stages / roofline / e2e / L2-cold of one layer on one GPU for the
+    tokens in h ([T, d] on the device)."""
+    tokens = h.shape[0]
+    step = lambda: block(h)
+    for _ in range(args.warmup):
+        y = step()
+    torch.cuda.synchronize()
+    moe.device_status()
+    soak_steps = soak(step)
+    ms_total = event_ms(step, args.steps)
+    ms_step = ms_total / args.steps
+    moe.device_status()
+    stage = stage_times(C, step, args.steps)
+    y = step()
+    out = {"value": tokens / (ms_step * 1e-3), "ms_per_step": ms_step, "stage_ms": stage,
+           "soak_steps_before_timing": soak_steps,
+           "roofline": roofline_single(syn, spec, tokens, stage, peaks)}
+    flops = syn.layer_flops(tokens, spec.top_k, spec.hidden, spec.ffn)
+    experts_active = min(spec.experts, tokens * spec.top_k)
+    layer_bytes = (experts_active * 3 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
+                   + 2 * tokens * spec.hidden * 2 + spec.experts * spec.hidden * 4)
+    out["whole_layer"] = {"tensor_frac": flops / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                          "hbm_frac": layer_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    regime = moe.REGIMES[args.regime]
+    e2e, y_host = e2e_pipeline(C, moe, block.layer, h, args.steps, regime, depth=2)
+    assert torch.equal(y_host, y.reshape(y_host.shape)), "host path and device path disagree"
+    one, _ = e2e_pipeline(C, moe, block.layer, h, args.steps, regime, depth=1)
+    e2e["one_step_at_a_time"] = one["value"]
+    out["e2e"] = e2e
+    if cold and tokens <= 512:
+        # L2-cold variant for the HBM-bound decode workloads: a 256 MB buffer
+        # (twice the L2) is rewritten before every step; each step has its own events
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=h.device)
+        pairs_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                    for _ in range(args.steps)]
+        for i, (a, b) in enumerate(pairs_ev):
+            flush.fill_(i & 0xFF)
+            a.record()
+            step()
+            b.record()
+        torch.cuda.synchronize()
+        t = sorted(a.elapsed_time(b) for a, b in pairs_ev)
+        cold_ms = t[len(t) // 2]
+        out["l2_cold"] = {"ms_per_step": cold_ms, "value": tokens / (cold_ms * 1e-3), "unit": "tokens/s",
+                          "hbm_frac": layer_bytes / (cold_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                          "flush_bytes": flush.numel(),
+                          "statistic": f"median of {args.steps} single-step timings"}
+        del flush
+        moe.device_status()
+    return out
 
 
 def main():
@@ -170,10 +393,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="prefill4096", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--regime", default="auto", choices=["auto", "stream", "tensor"])
+    ap.add_argument("--regime", default="auto", choices=["auto", "stream", "tensor", "tensor_pair"])
     ap.add_argument("--ep", default="p2p", choices=["p2p", "nccl"],
                     help="token exchange between ranks: peer-to-peer stores or NCCL all-to-all")
+    ap.add_argument("--tokens", type=int, default=0, help="profile_small only: token count")
+    ap.add_argument("--kind", default="Q8_0", choices=["Q8_0", "Q4_K"], help="profile_small only")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true")
     args = ap.parse_args()
     spec_name, tokens = WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -194,128 +420,111 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     from shark_platform_b200 import _cabi as C, moe, synthetic as syn
-    b200_block, device_input = syn.case_block, syn.case_input
-    spec = syn.CASES[spec_name]
-    if world > 1:
-        # every rank draws the same full layer on its own GPU (same seed, same
-        # generator) and keeps its expert shard: seconds instead of a minute of
-        # host-side generation per rank
-        import dataclasses
-        case = syn.make_case_on_device(dataclasses.replace(spec, tokens=tokens), dev)
-    else:
-        case = syn.make_case(spec, tokens=tokens)
     peaks = measured_peaks()
-    flops = syn.layer_flops(tokens, spec.top_k, spec.hidden, spec.ffn)
-    w_bytes_expert = 3 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
+    spec = syn.CASES[spec_name]
+    transport = args.ep
 
-    layers = 1
-    if args.workload == "stack32_decode64":
-        assert world == 1, "the layer stack runs on one GPU in this build"
-        from shark_platform_b200.moe import B200MoeStack
-        import dataclasses
-
-        layers = 32
-        blocks = []
-        for i in range(layers):
-            sp = dataclasses.replace(spec, tokens=tokens, router_bias="zipf", seed=1000 + i)
-            blocks.append(b200_block(syn.make_case_on_device(sp, dev), regime=args.regime, device=dev))
-        block = blocks[0]
-        stack = B200MoeStack(blocks)
-        h = device_input(case, dev).reshape(tokens, spec.hidden).contiguous()
-        step = lambda: stack(h)
-        fused = C.lib.b200moe_front_supported(tokens, ctypes.byref(block.layer.desc))
-        launches_per_step = (4 if fused else 6) * layers
-    elif world == 1:
-        block = b200_block(case, regime=args.regime, device=dev)
-        h = device_input(case, dev).reshape(tokens, spec.hidden).contiguous()
-        step = lambda: block(h)
-        # router, plan and permutation are one launch for small token counts
-        fused = C.lib.b200moe_front_supported(tokens, ctypes.byref(block.layer.desc))
-        launches_per_step = 4 if fused else 6
-    else:
-        from shark_platform_b200 import parallel
-
-        transport = args.ep
-        if transport == "p2p":
-            try:
-                block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime,
-                                                 transport="p2p")
-            except Exception as exc:  # symmetric memory not available on this machine
-                transport = f"nccl (p2p set-up failed: {type(exc).__name__}: {str(exc)[:120]})"
-                block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime)
-        else:
-            block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime)
-        per = tokens // world
-        h = device_input(case, dev).reshape(tokens, spec.hidden)[rank * per:(rank + 1) * per].contiguous()
-        step = lambda: block(h)
-        launches_per_step = block.launches_per_step
+    # ------------------------------------------------------------ profiler case
+    if args.workload == "profile_small":
+        tokens = args.tokens or tokens
+        sp = dataclasses.replace(spec, tokens=tokens, ffn=3584, kind=args.kind)
+        case = syn.make_case_on_device(sp, dev)
+        block = syn.case_block(case, args.regime, dev)
+        h = syn.case_input(case, dev).reshape(tokens, sp.hidden).contiguous()
+        for _ in range(args.warmup):
+            block(h)
+        torch.cuda.synchronize()
+        ms = event_ms(lambda: block(h), args.steps) / args.steps
+        moe.device_status()
+        print(json.dumps({"metric": "moe_layer_tokens_per_s", "value": tokens / (ms * 1e-3),
+                          "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+                          "config": {"workload": "profile_small", "tokens": tokens, "experts": sp.experts,
+                                     "hidden": sp.hidden, "ffn": sp.ffn, "kind": sp.kind,
+                                     "regime": args.regime}}), flush=True)
+        return
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        y = step()
-    barrier()
-    moe.device_status()
-
+    layers = 1
+    secondary = None
+    cpu = None
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+
+    # ----------------------------------------------------------- one GPU, one layer
+    if world == 1 and args.workload != "stack32_decode64":
+        case = syn.make_case(spec, tokens=tokens)
+        block = syn.case_block(case, args.regime, dev)
+        h = syn.case_input(case, dev).reshape(tokens, spec.hidden).contiguous()
+        fused = C.lib.b200moe_front_supported(tokens, ctypes.byref(block.layer.desc))
+        launches_per_step = 4 if fused else 6
         sampler.start()
-        time.sleep(0.3)  # let nvidia-smi come up so that it samples the timed region
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        y = step()
-    ev1.record()
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-    value = tokens * layers / (ms_step * 1e-3)
-    moe.device_status()
+        time.sleep(0.3)
+        m = measure_layer(C, moe, syn, block, h, spec, args, peaks)
+        clocks = sampler.stop()
+        clocks["window"] = (f"{SOAK_S} s of the same steps before the timed region, the timed region, the "
+                            "stage-event pass and the host-buffer passes")
+        if args.workload == "prefill4096" and not args.no_secondary:
+            # the other headline target, on the same layer in the same run
+            h32 = h[:32].contiguous()
+            s2 = ClockSampler(local_rank)
+            s2.start()
+            time.sleep(0.3)
+            m2 = measure_layer(C, moe, syn, block, h32, spec, args, peaks)
+            c2 = s2.stop()
+            secondary = {"decode32": {
+                "config": {"workload": "decode32", "tokens": 32, "note": "first 32 tokens of the same batch, same layer"},
+                "value": m2["value"], "unit": "tokens/s", "ms_per_step": m2["ms_per_step"],
+                "roofline": m2["roofline"], "whole_layer": m2["whole_layer"], "stage_ms": m2["stage_ms"],
+                "l2_cold": m2.get("l2_cold"), "e2e": m2["e2e"], "clocks": c2,
+                "gpu_launches": 4 * args.steps}}
+        if not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count() or 1)
+            sample = max(1, min(tokens, 128))
+            sub = dataclasses.replace(case, h=case.h[:, :sample].contiguous())
+            cl = CpuLayer(sub)
+            tps, _ = cl.time(sub.h, steps=1, warmup=0)
+            cpu = {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": cl.kind,
+                   "sample": f"the first {sample} tokens of the same batch, one pass ({CPU_CHUNK} tokens per "
+                             f"layer call), same layer on the host: {cl.how}"}
+        value, ms_step = m["value"], m["ms_per_step"]
+        e2e, roofline, stage, whole = m["e2e"], m["roofline"], m["stage_ms"], m["whole_layer"]
+        l2_cold = m.get("l2_cold")
+    elif world == 1:
+        # ------------------------------------------- 32-layer stack on one GPU
+        from shark_platform_b200.moe import B200MoeStack
 
-    # ---- same K steps again with CUDA events around every stage (the events
-    # cost a few microseconds per step, so they stay out of the timed region);
-    # if the timed region was too short for nvidia-smi's 100 ms period, this pass
-    # is repeated until the sampler has seen the same load for half a second
-    C.check(C.lib.b200moe_profile_enable(1))
-    if world > 1:
-        block.backend.profile = True
-    t_soak = time.perf_counter()
-    for _ in range(args.steps):
-        y = step()
-    torch.cuda.synchronize()
-    stage_ms = (ctypes.c_float * 6)()
-    calls = ctypes.c_int32(0)
-    C.check(C.lib.b200moe_profile_read(stage_ms, ctypes.byref(calls)))
-    C.check(C.lib.b200moe_profile_enable(0))
-    if world > 1:
-        block.backend.profile = False
-    soak_steps = 0
-    if world == 1:
-        while ms_total < 500.0 and time.perf_counter() - t_soak < 0.6:
-            y = step()
-            soak_steps += 1
-    elif ms_total < 500.0:
-        # every rank must run the same number of collective steps
-        soak_steps = max(1, min(2000, int(500.0 / max(ms_step, 1e-3))))
-        for _ in range(soak_steps):
-            y = step()
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    if clocks is not None:
-        clocks["window"] = ("timed region + stage-event pass" +
-                            (f" + {soak_steps} more steps of the same load" if soak_steps else ""))
-
-    # ---- end to end through the C ABI with host buffers (pinned), copies timed
-    e2e = None
-    if world == 1 and layers > 1:
+        layers = 32
+        blocks = []
+        for i in range(layers):
+            sp = dataclasses.replace(spec, tokens=tokens, router_bias="zipf", seed=1000 + i)
+            blocks.append(syn.case_block(syn.make_case_on_device(sp, dev), args.regime, dev))
+        stack = B200MoeStack(blocks)
+        case0 = syn.make_case_on_device(dataclasses.replace(spec, tokens=tokens, seed=999), dev)
+        h = syn.case_input(case0, dev).reshape(tokens, spec.hidden).contiguous()
+        step = lambda: stack(h)
+        fused = C.lib.b200moe_front_supported(tokens, ctypes.byref(blocks[0].layer.desc))
+        launches_per_step = (4 if fused else 6) * layers
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        moe.device_status()
+        sampler.start()
+        time.sleep(0.3)
+        soak(step)
+        ms_step = event_ms(step, args.steps) / args.steps
+        stage = stage_times(C, step, min(args.steps, 512 // layers))
+        clocks = sampler.stop()
+        clocks["window"] = f"{SOAK_S} s of the same steps before the timed region, the timed region, the stage-event pass"
+        moe.device_status()
+        value = tokens * layers / (ms_step * 1e-3)
+        roofline = roofline_single(syn, spec, tokens, stage, peaks)
+        layer_bytes = (spec.experts * 3 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
+                       + 2 * tokens * spec.hidden * 2 + spec.experts * spec.hidden * 4)
+        whole = {"hbm_frac": layers * layer_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]}
         hp = h.cpu().pin_memory()
         yp = torch.empty_like(hp).pin_memory()
         h_dev = torch.empty_like(h)
@@ -333,35 +542,108 @@ def main():
             e2e_step()
         dt = time.perf_counter() - t0
         e2e = {"value": tokens * layers * args.steps / dt, "unit": "tokens/s",
-               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
-    elif world == 1:
-        layer = block.layer
-        hp = h.cpu().pin_memory()
-        yp = torch.empty_like(hp).pin_memory()
-        nbytes = hp.numel() * hp.element_size()
-        dev_io = torch.empty(2 * (nbytes + 1024), dtype=torch.uint8, device=dev)
-        ws = layer.workspace(tokens)
-        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        regime = moe.REGIMES[args.regime]
-
-        def e2e_step():
-            C.check(C.lib.b200moe_layer_forward_host(
-                ctypes.byref(layer.desc), ctypes.c_void_p(hp.data_ptr()),
-                ctypes.c_void_p(yp.data_ptr()), C.DT_BF16, tokens, regime,
-                ctypes.c_void_p(dev_io.data_ptr()), ctypes.c_void_p(ws.data_ptr()), ws.numel(), st))
-            torch.cuda.current_stream().synchronize()
-
-        for _ in range(3):
-            e2e_step()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_step()
-        dt = time.perf_counter() - t0
-        assert torch.equal(yp.to(dev), y.reshape(yp.shape)), "host path and device path disagree"
-        e2e = {"value": tokens * args.steps / dt, "unit": "tokens/s",
-               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "steps_in_flight": 1}
+        l2_cold = None
     else:
+        # ------------------------------------------------ expert parallelism
+        from shark_platform_b200 import parallel
+
+        # every rank draws the same full layer on its own GPU (same seed) and keeps
+        # its expert shard: seconds instead of a minute of host-side generation
+        case = syn.make_case_on_device(dataclasses.replace(spec, tokens=tokens), dev)
+        per = tokens // world
+        h_all = syn.case_input(case, dev).reshape(tokens, spec.hidden)
+        h = h_all[rank * per:(rank + 1) * per].contiguous()
+        # correctness witness, outside the timed region: this rank's token slice
+        # through the single-GPU layer, before the other ranks' experts are dropped
+        full_block = syn.case_block(case, args.regime, dev)
+        y_single, ex_single, _ = full_block.layer.forward(h, want_routing=True)
+        y_single = y_single.clone()
+        del full_block
+        torch.cuda.empty_cache()
+        if transport == "p2p":
+            try:
+                block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime, transport="p2p")
+            except Exception as exc:  # symmetric memory not available on this machine
+                transport = f"nccl (p2p set-up failed: {type(exc).__name__}: {str(exc)[:120]})"
+                block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime)
+        else:
+            block = parallel.build_from_case(case, dist.group.WORLD, regime=args.regime)
+        del case
+        torch.cuda.empty_cache()
+        step = lambda: block(h)
+        launches_per_step = block.launches_per_step
+        y = step()
+        num = torch.linalg.norm((y.float() - y_single.float()).double()) ** 2
+        den = torch.linalg.norm(y_single.float().double()) ** 2
+        agg = torch.stack([num, den])
+        dist.all_reduce(agg)
+        ep_check = {"rel_l2_vs_single_gpu": float(torch.sqrt(agg[0] / agg[1])),
+                    "what": "every rank's own token slice through the full single-GPU layer vs the "
+                            "expert-parallel result, all ranks' tokens together"}
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        moe.device_status()
+        if rank == 0:
+            sampler.start()
+            time.sleep(0.3)
+        # the same number of soak steps on every rank (collective steps)
+        t0 = time.perf_counter()
+        step()
+        torch.cuda.synchronize()
+        n_soak = torch.tensor([max(8, int(SOAK_S / max(time.perf_counter() - t0, 1e-4)))], device=dev)
+        dist.all_reduce(n_soak, op=dist.ReduceOp.MIN)
+        for _ in range(min(int(n_soak.item()), 4000)):
+            step()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            y = step()
+        ev1.record()
+        barrier()
+        t = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item()) / args.steps
+        value = tokens / (ms_step * 1e-3)
+        moe.device_status()
+        if isinstance(block, parallel.P2PExpertParallelMoeBlock):
+            st_ms = stage_times(C, step, args.steps)  # per-stage events inside the C call
+            gu_ms, dn_ms = st_ms["gate_up"], st_ms["down"]
+        else:
+            block.backend.profile = True
+            for _ in range(args.steps):
+                step()
+            torch.cuda.synchronize()
+            block.backend.profile = False
+            tm = block.backend.timings
+            gu_ms = sum(ev[0].elapsed_time(ev[1]) for ev, _ in tm) / max(len(tm), 1)
+            dn_ms = sum(ev[1].elapsed_time(ev[2]) for ev, _ in tm) / max(len(tm), 1)
+            st_ms = {}
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+        if clocks is not None:
+            clocks["window"] = f"~{SOAK_S} s of the same steps before the timed region, the timed region, the stage-event pass"
+        # gate/up kernel on every rank: flops of all routed rows over the slowest
+        # rank's mean kernel time, against N x the single-GPU peak
+        tt = torch.tensor([gu_ms, dn_ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        gu_flops = float(tokens * spec.top_k) * 2 * 2 * spec.ffn * spec.hidden
+        ach = gu_flops / (float(tt[0].item()) * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"] * world
+        roofline = {"bound": "tensor", "kernel": "gate_up", "achieved": ach, "peak": peak,
+                    "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                    "peak_source": peaks["source"] + f" (cuBLAS bf16 burst x {world} GPUs)"}
+        stage = {"gate_up_max_over_ranks": float(tt[0].item()), "down_max_over_ranks": float(tt[1].item()),
+                 "rank0": st_ms}
+        flops = syn.layer_flops(tokens, spec.top_k, spec.hidden, spec.ffn)
+        whole = {"tensor_frac": flops / (ms_step * 1e-3) / 1e12 / peak, "ep_check": ep_check}
+        # load balance: rows each rank's experts received
+        rows = torch.bincount(ex_single.reshape(-1).to(torch.int64), minlength=spec.experts).float()
+        dist.all_reduce(rows)
+        per_rank = rows.view(world, -1).sum(dim=1)
+        whole["rows_per_rank"] = {"max": float(per_rank.max()), "mean": float(per_rank.mean())}
         hp = h.cpu().pin_memory()
         yp = torch.empty_like(hp).pin_memory()
         h_dev = torch.empty_like(h)
@@ -369,8 +651,7 @@ def main():
 
         def e2e_step():
             h_dev.copy_(hp, non_blocking=True)
-            yy = block(h_dev)
-            yp.copy_(yy, non_blocking=True)
+            yp.copy_(block(h_dev), non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
         for _ in range(3):
@@ -383,102 +664,28 @@ def main():
         dt = torch.tensor([time.perf_counter() - t0], device=dev)
         dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         e2e = {"value": tokens * args.steps / float(dt.item()), "unit": "tokens/s",
-               "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": nbytes * world}
-
-    # ---- roofline of the dominant kernel (gate/up), from the stage events
-    n_calls = max(int(calls.value), 1)
-    stage = {n: stage_ms[i] / n_calls for i, n in enumerate(STAGES)}
-    if world == 1:
-        experts_active = min(spec.experts, tokens * spec.top_k)
-        if tokens >= 512:
-            gu_flops = tokens * spec.top_k * 2 * 2 * spec.ffn * spec.hidden
-            ach = gu_flops / (stage["gate_up"] * 1e-3) / 1e12
-            peak = peaks["bf16_tflops"]
-            roofline = {"bound": "tensor", "kernel": "gate_up", "achieved": ach, "peak": peak,
-                        "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-                        "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
-                        "peak_source": peaks["source"] + " (cuBLAS bf16 burst)"}
-        else:
-            gu_bytes = experts_active * 2 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
-            ach = gu_bytes / (stage["gate_up"] * 1e-3) / 1e9
-            peak = peaks["hbm_gbs"]
-            # DRAM traffic of this kernel per launch: an ncu capture of a 374 MB case of
-            # the same kernel read 1.0028 x its quantised bytes; traffic grows with them
-            roofline = {"bound": "hbm", "kernel": "gate_up", "achieved": ach, "peak": peak,
-                        "unit": "GB/s", "frac": ach / peak, "traffic": gu_bytes * 1.0028,
-                        "peak_source": peaks["source"] + " (copy)"}
-        layer_bytes = experts_active * w_bytes_expert + 2 * tokens * spec.hidden * 2 + spec.experts * spec.hidden * 4
-        whole = {"tensor_frac": layers * flops / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
-                 "hbm_frac": layers * layer_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-    else:
-        # gate/up kernel on every rank: flops of the rows each rank received over
-        # the slowest rank's mean kernel time, against N x the single-GPU peak
-        tm = block.backend.timings
-        gu_ms = sum(ev[0].elapsed_time(ev[1]) for ev, _ in tm) / max(len(tm), 1)
-        rows = sum((n if n >= 0 else tokens * spec.top_k / world) for _, n in tm) / max(len(tm), 1)
-        t = torch.tensor([gu_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        r = torch.tensor([rows], device=dev)
-        dist.all_reduce(r, op=dist.ReduceOp.SUM)
-        gu_flops = float(r.item()) * 2 * 2 * spec.ffn * spec.hidden
-        ach = gu_flops / (float(t.item()) * 1e-3) / 1e12
-        peak = peaks["bf16_tflops"] * world
-        roofline = {"bound": "tensor", "kernel": "gate_up", "achieved": ach, "peak": peak,
-                    "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-                    "peak_source": peaks["source"] + f" (cuBLAS bf16 burst x {world} GPUs)"}
-        stage = {"gate_up_max_over_ranks": float(t.item())}
-        whole = {"tensor_frac": flops / (ms_step * 1e-3) / 1e12 / peak}
-
-    # ---- L2-cold variant for the HBM-bound decode workloads: a 256 MB buffer
-    # (twice the L2) is rewritten before every step; each step has its own events
-    l2_cold = None
-    if world == 1 and layers == 1 and tokens <= 512:
-        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-        pairs_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                    for _ in range(args.steps)]
-        for i, (a, b) in enumerate(pairs_ev):
-            flush.fill_(i & 0xFF)
-            a.record()
-            y = step()
-            b.record()
-        torch.cuda.synchronize()
-        cold = sorted(a.elapsed_time(b) for a, b in pairs_ev)
-        cold_ms = cold[len(cold) // 2]
-        l2_cold = {"ms_per_step": cold_ms, "value": tokens / (cold_ms * 1e-3), "unit": "tokens/s",
-                   "flush_bytes": flush.numel(), "statistic": f"median of {args.steps} single-step timings"}
-        del flush
-        moe.device_status()
-
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        torch.set_num_threads(os.cpu_count() or 1)
-        sample = min(tokens, 8)
-        params, hs, _ = cpu_reference_setup(case, sample)
-        tps, _ = time_cpu(params, hs, steps=3, warmup=1)
-        cpu = {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-               "sample": f"{sample} tokens x 3 steps of the same layer on the host (torch-eager "
-                         f"gather + batched-GEMV form of the reference, dequantised weights)"}
+               "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": nbytes * world,
+               "steps_in_flight": 1}
+        l2_cold = None
 
     if rank == 0:
+        sm = clocks.get("sm_mhz") if clocks else None
         out = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 operands (exact Q8_0 dequant), f32 accumulate, bf16 activations in/out",
             "data": "synthetic",
-            "config": {"workload": args.workload,
-                       "layer": f"{spec_name} MoE FFN ({spec.kind} experts, {spec.activation})"
-                                + (f", stack of {layers} layers, value = layer-tokens/s" if layers > 1 else ""),
-                       "tokens": tokens, "hidden": spec.hidden, "ffn": spec.ffn,
-                       "experts": spec.experts, "top_k": spec.top_k, "regime": args.regime,
-                       "parallelism": "single GPU" if world == 1 else f"ep{world}, exchange: {transport}",
-                       "l2": "expert weights (>= 0.8 GB per layer) exceed L2 (126 MB); no flush"},
+            "config": workload_config(args, spec_name, spec, tokens, layers, world, transport),
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
-            "clocks": clocks, "roofline": roofline, "stage_ms": stage, "whole_layer": whole,
+            "clocks": clocks, "ms_x_mhz": (ms_step * sm) if sm else None,
+            "roofline": roofline, "stage_ms": stage, "whole_layer": whole,
             "cpu_baseline": cpu,
         }
         if l2_cold is not None:
             out["l2_cold"] = l2_cold
+        if secondary is not None:
+            out["secondary"] = secondary
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()

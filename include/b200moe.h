@@ -278,6 +278,29 @@ int b200moe_ep_return(const b200moe_ep_t* ep, const float* d_rows, int32_t kspli
                       int32_t cap_rows, const int32_t* seg2, int32_t hidden, int32_t ret_rows,
                       void* stream);
 
+/* The whole expert-parallel layer from one call (no reference counterpart; the
+ * layer semantics are MoeBlock.forward, layers/mixture_of_experts_block.py:
+ * 64-90): router -> route plan -> publish counts -> barrier -> dispatch ->
+ * barrier -> gate/up -> down -> return -> barrier -> combine, all enqueued on
+ * `stream` without touching the host in between.  `layer` holds THIS rank's
+ * expert shard (gate/up/down with experts_local experts, expert_begin = rank *
+ * experts_local, layer->experts = all experts); h, y: this rank's own tokens
+ * [tokens, d].  cap_rows / ret_rows are the row capacities of ep->recv_x and
+ * ep->ret_y; max_segment bounds the rows any one local expert can receive;
+ * ksplit = b200moe_down_ksplit(&layer->down, expected rows, max_segment,
+ * regime).  The call uses barrier epochs epoch+1 .. epoch+3: pass 0 first and
+ * add 3 per call, identically on every rank, across all layers that share the
+ * exchange buffers.  A rank with no tokens still calls (it owns experts).
+ * While b200moe_profile_enable is on, the six recorded stages are router | plan +
+ * publish + barrier | dispatch + barrier | gate/up | down | return + barrier +
+ * combine. */
+size_t b200moe_ep_workspace_bytes(const b200moe_layer_t* layer, int32_t tokens, int32_t cap_rows,
+                                  int32_t ksplit);
+int b200moe_ep_layer_forward(const b200moe_layer_t* layer, const b200moe_ep_t* ep, const void* h,
+                             void* y, int io_dtype, int32_t tokens, int regime, int32_t cap_rows,
+                             int32_t ret_rows, int32_t max_segment, int32_t ksplit, int32_t epoch,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* Bytes of workspace b200moe_layer_forward needs for up to `tokens` tokens. */
 size_t b200moe_workspace_bytes(const b200moe_layer_t* layer, int32_t tokens);
 
@@ -294,6 +317,39 @@ int b200moe_layer_forward(const b200moe_layer_t* layer, const void* h, void* y, 
 int b200moe_layer_forward_host(const b200moe_layer_t* layer, const void* h_host, void* y_host,
                                int io_dtype, int32_t tokens, int regime, void* dev_io,
                                void* workspace, size_t workspace_bytes, void* stream);
+
+/* A stream of batches from host memory (no reference counterpart: the
+ * reference's eager layer takes whatever device its tensors are on).  The
+ * pipeline keeps `depth` steps in flight: the host->device copy of a step's
+ * input, the layer, and the device->host copy of its output run on three
+ * streams linked by events, so consecutive steps overlap and the sustained rate
+ * is the layer's own as long as a copy is shorter than the layer.  Pinned host
+ * buffers are required for the copies to be asynchronous.
+ *   b200moe_pipeline_bytes   device memory the caller must provide (2*depth
+ *                            activation buffers of max_tokens rows + the workspace)
+ *   b200moe_pipeline_create  builds the pipeline on the current device; creates
+ *                            two streams and 3*depth events, allocates no
+ *                            device memory; the layer descriptor is copied
+ *   b200moe_pipeline_submit  enqueues one step (h_host -> layer -> y_host); the
+ *                            layer runs on `stream`.  Returns without waiting,
+ *                            except that it first waits for the output copy of
+ *                            the step that used the same slot `depth` submits
+ *                            ago.  y_host is complete after a later submit has
+ *                            reused its slot or after b200moe_pipeline_drain.
+ *                            h_host / y_host must stay untouched until then.
+ *   b200moe_pipeline_drain   waits for every submitted step's output copy
+ *   b200moe_pipeline_destroy drains, then frees the streams and events
+ * Not thread-safe: one thread drives one pipeline. */
+typedef struct b200moe_pipeline b200moe_pipeline_t;
+size_t b200moe_pipeline_bytes(const b200moe_layer_t* layer, int io_dtype, int32_t max_tokens,
+                              int32_t depth);
+int b200moe_pipeline_create(const b200moe_layer_t* layer, int io_dtype, int32_t max_tokens,
+                            int regime, int32_t depth, void* dev_mem, size_t dev_bytes,
+                            b200moe_pipeline_t** out);
+int b200moe_pipeline_submit(b200moe_pipeline_t* p, const void* h_host, void* y_host,
+                            int32_t tokens, void* stream);
+int b200moe_pipeline_drain(b200moe_pipeline_t* p);
+int b200moe_pipeline_destroy(b200moe_pipeline_t* p);
 
 /* Stage timing for benchmarks (no reference counterpart).  While enabled,
  * b200moe_layer_forward brackets each of its six stages (router, route plan,

@@ -114,9 +114,17 @@ _PROTOS = {
     "b200moe_ep_barrier": (c_int, [POINTER(EpDesc), c_int32, _P, _P]),
     "b200moe_ep_dispatch": (c_int, [POINTER(EpDesc), _P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32, _P]),
     "b200moe_ep_return": (c_int, [POINTER(EpDesc), _P, c_int32, c_int32, _P, c_int32, c_int32, _P]),
+    "b200moe_ep_workspace_bytes": (c_size_t, [_L, c_int32, c_int32, c_int32]),
+    "b200moe_ep_layer_forward": (c_int, [_L, POINTER(EpDesc), _P, _P, c_int, c_int32, c_int, c_int32, c_int32,
+                                         c_int32, c_int32, c_int32, _P, c_size_t, _P]),
     "b200moe_workspace_bytes": (c_size_t, [_L, c_int32]),
     "b200moe_layer_forward": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, c_size_t, _P, _P, _P]),
     "b200moe_layer_forward_host": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, _P, c_size_t, _P]),
+    "b200moe_pipeline_bytes": (c_size_t, [_L, c_int, c_int32, c_int32]),
+    "b200moe_pipeline_create": (c_int, [_L, c_int, c_int32, c_int, c_int32, _P, c_size_t, POINTER(c_void_p)]),
+    "b200moe_pipeline_submit": (c_int, [_P, _P, _P, c_int32, _P]),
+    "b200moe_pipeline_drain": (c_int, [_P]),
+    "b200moe_pipeline_destroy": (c_int, [_P]),
     "b200moe_profile_enable": (c_int, [c_int]),
     "b200moe_profile_read": (c_int, [POINTER(c_float), POINTER(c_int32)]),
 }

@@ -489,6 +489,119 @@ int b200moe_layer_forward_host(const b200moe_layer_t* L, const void* h_host, voi
   return B200MOE_OK;
 }
 
+// ---- expert parallelism: the whole per-layer sequence from one call ---------
+namespace {
+struct EpWorkspace {
+  __half* xn;
+  int32_t* experts;
+  float* gates;
+  int32_t* counts;
+  int32_t* seg;
+  int32_t* perm;
+  int32_t* inv;
+  int32_t* seg2;
+  __half* a;
+  float* dpart;
+  size_t bytes;
+};
+
+EpWorkspace ep_carve(const b200moe_layer_t* L, int tokens, int cap_rows, int ksplit, void* base) {
+  const size_t T = tokens > 0 ? tokens : 1;
+  const size_t P = T * L->top_k;
+  const size_t R = cap_rows > 0 ? cap_rows : 1;
+  uint8_t* p = static_cast<uint8_t*>(base);
+  size_t off = 0;
+  auto take = [&](size_t n) {
+    void* r = p ? p + off : nullptr;
+    off += align_up(n, 1024);
+    return r;
+  };
+  EpWorkspace w;
+  w.xn = static_cast<__half*>(take(T * L->hidden * 2));
+  w.experts = static_cast<int32_t*>(take(P * 4));
+  w.gates = static_cast<float*>(take(P * 4));
+  w.counts = static_cast<int32_t*>(take(64 * 4));
+  w.seg = static_cast<int32_t*>(take(65 * 4));
+  w.perm = static_cast<int32_t*>(take(P * 4));
+  w.inv = static_cast<int32_t*>(take(P * 4));
+  w.seg2 = static_cast<int32_t*>(take(65 * 4));
+  w.a = static_cast<__half*>(take(R * L->ffn * 2));
+  w.dpart = static_cast<float*>(take(static_cast<size_t>(ksplit) * R * L->hidden * 4));
+  w.bytes = off;
+  return w;
+}
+}  // namespace
+
+size_t b200moe_ep_workspace_bytes(const b200moe_layer_t* layer, int32_t tokens, int32_t cap_rows,
+                                  int32_t ksplit) {
+  if (layer == nullptr || tokens < 0 || cap_rows < 0 || ksplit < 1) return 0;
+  return ep_carve(layer, tokens, cap_rows, ksplit, nullptr).bytes;
+}
+
+int b200moe_ep_layer_forward(const b200moe_layer_t* L, const b200moe_ep_t* ep, const void* h, void* y,
+                             int io_dtype, int32_t tokens, int regime, int32_t cap_rows,
+                             int32_t ret_rows, int32_t max_segment, int32_t ksplit, int32_t epoch,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  B200_REQUIRE(ep != nullptr, "ep_layer_forward: NULL exchange descriptor");
+  B200_REQUIRE(ep->world >= 1 && ep->rank >= 0 && ep->rank < ep->world && ep->world <= 16,
+               "ep_layer_forward: world %d / rank %d out of range", ep->world, ep->rank);
+  B200_REQUIRE(L->gate.experts == ep->experts_local && L->experts == ep->experts_local * ep->world &&
+                   L->expert_begin == ep->rank * ep->experts_local,
+               "ep_layer_forward: the layer must hold this rank's expert shard "
+               "(experts_local %d, begin %d of %d)", L->gate.experts, L->expert_begin, L->experts);
+  B200_REQUIRE(tokens >= 0 && cap_rows >= 1 && ksplit >= 1 && max_segment >= 1,
+               "ep_layer_forward: bad sizes");
+  B200_REQUIRE(tokens * L->top_k <= ret_rows, "ep_layer_forward: %d pairs exceed the return buffer (%d rows)",
+               tokens * L->top_k, ret_rows);
+  B200_REQUIRE(io_dtype == B200MOE_DT_F32 || io_dtype == B200MOE_DT_BF16,
+               "ep_layer_forward: activations must be fp32 or bf16");
+  B200_REQUIRE((tokens == 0 || (h && y)) && workspace, "ep_layer_forward: NULL buffer");
+  EpWorkspace w = ep_carve(L, tokens, cap_rows, ksplit, workspace);
+  if (w.bytes > workspace_bytes) {
+    set_error("ep_layer_forward: workspace needs %zu bytes, got %zu", w.bytes, workspace_bytes);
+    return B200MOE_ERR_WORKSPACE;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int pairs = tokens * L->top_k;
+  const int E = L->experts;
+  const int pc = (g_prof.on && g_prof.used < PROF_CALLS) ? g_prof.used++ : -1;
+  const int kp_in = b200moe_kperm(L->gate.layout, regime, max_segment);
+  const int kp_mid = b200moe_kperm(L->down.layout, regime, max_segment);
+  void* recv_x = ep->recv_x[ep->rank];
+  void* ret_y = ep->ret_y[ep->rank];
+  // every rank takes part in every barrier, also one that has no tokens
+  prof_mark(pc, 0, st);
+  if (tokens > 0)
+    if (int rc = launch_router(h, io_dtype, tokens, L, w.xn, w.experts, w.gates, st)) return rc;
+  prof_mark(pc, 1, st);
+  if (int rc = launch_route_plan(w.experts, pairs, 0, E, w.counts, w.seg, w.perm, w.inv, st)) return rc;
+  if (int rc = b200moe_ep_publish_counts(ep, w.counts, stream)) return rc;
+  if (int rc = b200moe_ep_barrier(ep, epoch + 1, w.seg2, stream)) return rc;
+  prof_mark(pc, 2, st);
+  if (int rc = b200moe_ep_dispatch(ep, w.xn, w.experts, w.perm, w.seg, pairs, L->top_k, L->hidden, kp_in,
+                                   cap_rows, stream))
+    return rc;
+  if (int rc = b200moe_ep_barrier(ep, epoch + 2, nullptr, stream)) return rc;
+  prof_mark(pc, 3, st);
+  if (int rc = b200moe_gate_up(recv_x, w.seg2, cap_rows, max_segment, &L->gate, &L->up, L->activation,
+                               regime, kp_mid, w.a, stream))
+    return rc;
+  prof_mark(pc, 4, st);
+  if (int rc = b200moe_down(w.a, w.seg2, cap_rows, max_segment, &L->down, regime, ksplit, w.dpart, stream))
+    return rc;
+  prof_mark(pc, 5, st);
+  if (int rc = b200moe_ep_return(ep, w.dpart, ksplit, cap_rows, w.seg2, L->hidden, ret_rows, stream))
+    return rc;
+  if (int rc = b200moe_ep_barrier(ep, epoch + 3, nullptr, stream)) return rc;
+  if (tokens > 0)
+    if (int rc = launch_combine(ret_y, B200MOE_DT_BF16, 1, pairs, w.inv, w.gates, h, io_dtype, tokens, L, 1,
+                                y, io_dtype, st))
+      return rc;
+  prof_mark(pc, 6, st);
+  return B200MOE_OK;
+}
+
 int b200moe_profile_enable(int on) {
   if (on && !g_prof.created) {
     for (int c = 0; c < PROF_CALLS; ++c)

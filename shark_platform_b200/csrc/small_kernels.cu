@@ -196,106 +196,102 @@ __device__ __forceinline__ void router_select(const float* logit, int lane, int 
   }
 }
 
-// Prefill: four tokens per warp.  With one token per warp every warp streams
-// the whole router weight (E x d fp32) out of L2 for itself, 4096 tokens x 128 KB
-// for a Mixtral layer; sharing each weight vector between four tokens cuts that
-// to a quarter.  Per token the operations and their order are those of
-// router_kernel, so experts and gates are bit-identical.
-constexpr int RM_WARPS = 4;
-constexpr int RM_TOK = 4;
+// Prefill: persistent CTAs with the router weight and the norm weight resident
+// in shared memory.  With one token per warp reading them from global memory,
+// every warp streams the whole router weight (E x d fp32) out of L2 for itself:
+// 4096 tokens x 128 KB for a Mixtral layer, which is what that kernel's time is.
+// Here a CTA loads them once (E*d*4 + d*4 bytes, up to ~220 KB) and its eight
+// warps walk over the tokens; only the activations move through HBM.  Per token
+// the operations and their order are those of router_kernel, so experts and gates
+// are bit-identical to it.
+//
+// Shared layout: element j = 256*it + 8*lane + 4*hf + i of a vector is stored at
+// ((it*2 + hf)*32 + lane)*4 + i, so that the two 16-byte reads a lane makes per
+// step are conflict-free.
+constexpr int RS_WARPS = 8;
 
 template <typename T>
-__global__ void __launch_bounds__(RM_WARPS * 32)
-router_multi_kernel(const T* __restrict__ h, int tokens, int d, int E, int k, float eps,
-                    const float* __restrict__ norm_w, const float* __restrict__ rw,
-                    const float* __restrict__ rb, __half* __restrict__ xn_out,
-                    int32_t* __restrict__ experts_out, float* __restrict__ gates_out) {
-  __shared__ float s_logit[RM_WARPS][RM_TOK][MAX_EXPERTS];
+__global__ void __launch_bounds__(RS_WARPS * 32)
+router_smem_kernel(const T* __restrict__ h, int tokens, int d, int E, int k, float eps,
+                   const float* __restrict__ norm_w, const float* __restrict__ rw,
+                   const float* __restrict__ rb, __half* __restrict__ xn_out,
+                   int32_t* __restrict__ experts_out, float* __restrict__ gates_out) {
+  extern __shared__ float s_dyn[];
+  float* s_w = s_dyn;                       // [E][d] in the layout above
+  float* s_n = s_dyn + static_cast<size_t>(E) * d;  // [d]
+  float* s_logit = s_n + d;                 // [RS_WARPS][MAX_EXPERTS]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = (blockIdx.x * RM_WARPS + warp) * RM_TOK;
-  if (t0 >= tokens) return;
-  const int nt = min(RM_TOK, tokens - t0);
-
-  float rstd[RM_TOK];
-  {
-    float ss[RM_TOK];
-#pragma unroll
-    for (int q = 0; q < RM_TOK; ++q) ss[q] = 0.f;
-    for (int j = lane * 8; j < d; j += 256) {
-#pragma unroll
-      for (int q = 0; q < RM_TOK; ++q) {
-        if (q < nt) {
-          float v[8];
-          load8<T>(h + static_cast<size_t>(t0 + q) * d + j, v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) ss[q] = fmaf(v[i], v[i], ss[q]);
-        }
-      }
-    }
-#pragma unroll
-    for (int q = 0; q < RM_TOK; ++q) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss[q] += __shfl_xor_sync(0xffffffffu, ss[q], o);
-      rstd[q] = 1.0f / sqrtf(ss[q] / static_cast<float>(d) + eps);
-    }
+  auto slot = [](int j) { return (((j >> 8) * 2 + ((j >> 2) & 1)) * 32 + ((j >> 3) & 31)) * 4 + (j & 3); };
+  for (int idx = threadIdx.x * 4; idx < E * d; idx += RS_WARPS * 32 * 4) {
+    const int e = idx / d, j = idx - e * d;
+    *reinterpret_cast<float4*>(s_w + static_cast<size_t>(e) * d + slot(j)) =
+        *reinterpret_cast<const float4*>(rw + idx);
   }
+  for (int j = threadIdx.x * 4; j < d; j += RS_WARPS * 32 * 4)
+    *reinterpret_cast<float4*>(s_n + slot(j)) = *reinterpret_cast<const float4*>(norm_w + j);
+  __syncthreads();
 
-  for (int e0 = 0; e0 < E; e0 += 8) {
-    float acc[RM_TOK][8];
-#pragma unroll
-    for (int q = 0; q < RM_TOK; ++q)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
+  for (int t = blockIdx.x * RS_WARPS + warp; t < tokens; t += gridDim.x * RS_WARPS) {
+    const T* row = h + static_cast<size_t>(t) * d;
+    float ss = 0.f;
     for (int j = lane * 8; j < d; j += 256) {
-      float w[8], v[RM_TOK][8];
-      load8<float>(norm_w + j, w);
+      float v[8];
+      load8<T>(row + j, v);
 #pragma unroll
-      for (int q = 0; q < RM_TOK; ++q) {
-        if (q < nt) {
-          load8<T>(h + static_cast<size_t>(t0 + q) * d + j, v[q]);
+      for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+    }
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[q][i] = w[i] * (v[q][i] * rstd[q]);
-          if (e0 == 0) {
-            uint32_t packed[4];
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = 1.0f / sqrtf(ss / static_cast<float>(d) + eps);
+
+    for (int e0 = 0; e0 < E; e0 += 8) {
+      float acc[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              packed[i] = h2_as_u32(__halves2half2(to_half_sat(v[q][2 * i]), to_half_sat(v[q][2 * i + 1])));
-            *reinterpret_cast<uint4*>(xn_out + static_cast<size_t>(t0 + q) * d + j) =
-                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int j = lane * 8; j < d; j += 256) {
+        float v[8], w[8];
+        load8<T>(row + j, v);  // second pass: the row is in L1/L2
+        const int base = ((j >> 8) * 2 * 32 + lane) * 4;  // hf = 0; hf = 1 is 128 floats further
+        {
+          const float4 a = *reinterpret_cast<const float4*>(s_n + base);
+          const float4 b = *reinterpret_cast<const float4*>(s_n + base + 128);
+          w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+          w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = w[i] * (v[i] * rstd);
+        if (e0 == 0) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            packed[i] = h2_as_u32(__halves2half2(to_half_sat(v[2 * i]), to_half_sat(v[2 * i + 1])));
+          *reinterpret_cast<uint4*>(xn_out + static_cast<size_t>(t) * d + j) =
+              make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (e0 + e < E) {
+            const float* wr = s_w + static_cast<size_t>(e0 + e) * d + base;
+            const float4 a = *reinterpret_cast<const float4*>(wr);
+            const float4 b = *reinterpret_cast<const float4*>(wr + 128);
+            const float r[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[e] = fmaf(v[i], r[i], acc[e]);
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) v[q][i] = 0.f;
         }
       }
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        if (e0 + e < E) {
-          float r[8];
-          load8<float>(rw + static_cast<size_t>(e0 + e) * d + j, r);
 #pragma unroll
-          for (int q = 0; q < RM_TOK; ++q)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[q][e] = fmaf(v[q][i], r[i], acc[q][e]);
-        }
+        for (int o = 16; o > 0; o >>= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+        if (lane == 0 && e0 + e < E)
+          s_logit[warp * MAX_EXPERTS + e0 + e] = acc[e] + (rb ? rb[e0 + e] : 0.f);
       }
     }
-#pragma unroll
-    for (int q = 0; q < RM_TOK; ++q) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc[q][e] += __shfl_xor_sync(0xffffffffu, acc[q][e], o);
-        if (lane == 0 && e0 + e < E) s_logit[warp][q][e0 + e] = acc[q][e] + (rb ? rb[e0 + e] : 0.f);
-      }
-    }
-  }
-  __syncwarp();
-#pragma unroll
-  for (int q = 0; q < RM_TOK; ++q) {
-    if (q < nt)
-      router_select(s_logit[warp][q], lane, E, k, experts_out + static_cast<size_t>(t0 + q) * k,
-                    gates_out + static_cast<size_t>(t0 + q) * k);
+    __syncwarp();
+    router_select(s_logit + warp * MAX_EXPERTS, lane, E, k, experts_out + static_cast<size_t>(t) * k,
+                  gates_out + static_cast<size_t>(t) * k);
+    __syncwarp();  // the logits are rewritten for the warp's next token
   }
 }
 
@@ -636,16 +632,28 @@ int launch_router(const void* h, int h_dtype, int tokens, const b200moe_layer_t*
     B200_CHECK_CUDA(cudaGetLastError());
     return B200MOE_OK;
   }
-  if (tokens >= 1024) {
-    const int per_cta = RM_WARPS * RM_TOK;
-    dim3 mgrid((tokens + per_cta - 1) / per_cta), mblock(RM_WARPS * 32);
+  const size_t rs_smem = (static_cast<size_t>(L->experts) * L->hidden + L->hidden +
+                          RS_WARPS * MAX_EXPERTS) * sizeof(float);
+  if (tokens >= 1024 && rs_smem <= 227 * 1024) {
+    static bool configured[16][2] = {};
+    int dev = 0;
+    B200_CHECK_CUDA(cudaGetDevice(&dev));
+    const int ti = h_dtype == B200MOE_DT_F32 ? 0 : 1;
+    if (dev < 16 && !configured[dev][ti]) {
+      B200_CHECK_CUDA(cudaFuncSetAttribute(
+          ti == 0 ? reinterpret_cast<const void*>(&router_smem_kernel<float>)
+                  : reinterpret_cast<const void*>(&router_smem_kernel<__nv_bfloat16>),
+          cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+      configured[dev][ti] = true;
+    }
+    const int ctas = min(sm_count(), (tokens + RS_WARPS - 1) / RS_WARPS);
     if (h_dtype == B200MOE_DT_F32)
-      router_multi_kernel<float><<<mgrid, mblock, 0, st>>>(
+      router_smem_kernel<float><<<ctas, RS_WARPS * 32, rs_smem, st>>>(
           static_cast<const float*>(h), tokens, L->hidden, L->experts, L->top_k, L->rms_epsilon,
           L->ffn_norm_weight, L->router_weight, L->router_bias, static_cast<__half*>(xn), experts,
           gates);
     else
-      router_multi_kernel<__nv_bfloat16><<<mgrid, mblock, 0, st>>>(
+      router_smem_kernel<__nv_bfloat16><<<ctas, RS_WARPS * 32, rs_smem, st>>>(
           static_cast<const __nv_bfloat16*>(h), tokens, L->hidden, L->experts, L->top_k,
           L->rms_epsilon, L->ffn_norm_weight, L->router_weight, L->router_bias,
           static_cast<__half*>(xn), experts, gates);

@@ -284,6 +284,57 @@ class PreparedLayer:
         return (y, experts, gates) if want_routing else y
 
 
+class HostPipeline:
+    """Batches that live in (pinned) host memory, streamed through one layer
+    with `depth` steps in flight: a step's input copy, its kernels and its
+    output copy run on three streams, so consecutive steps overlap
+    (`b200moe_pipeline_*`).  `submit(h_host, y_host)` returns at once; `y_host`
+    is complete after `drain()` or once `depth` further steps were submitted."""
+
+    def __init__(self, layer: PreparedLayer, max_tokens: int, dtype: torch.dtype, depth: int = 2,
+                 regime: int = C.REGIME_AUTO):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise C.B200MoeError(f"activations must be fp32 or bf16, got {dtype}")
+        self.layer, self.dtype, self.max_tokens = layer, dtype, max_tokens
+        nbytes = C.lib.b200moe_pipeline_bytes(ctypes.byref(layer.desc), _DT[dtype], max_tokens, depth)
+        if nbytes == 0:
+            raise C.B200MoeError("pipeline: bad size or depth (1..8)")
+        self._mem = torch.empty(nbytes, dtype=torch.uint8, device=layer.device)
+        self._handle = ctypes.c_void_p()
+        with torch.cuda.device(layer.device):
+            C.check(C.lib.b200moe_pipeline_create(ctypes.byref(layer.desc), _DT[dtype], max_tokens, regime,
+                                                  depth, _ptr(self._mem), nbytes,
+                                                  ctypes.byref(self._handle)), "pipeline_create")
+        self._keep = []
+
+    def submit(self, h_host: torch.Tensor, y_host: torch.Tensor):
+        if h_host.is_cuda or y_host.is_cuda:
+            raise C.B200MoeError("pipeline buffers live in host memory")
+        if h_host.dtype != self.dtype or y_host.dtype != self.dtype or not (
+                h_host.is_contiguous() and y_host.is_contiguous()):
+            raise C.B200MoeError("pipeline buffers must be contiguous and of the pipeline's dtype")
+        tokens = h_host.numel() // self.layer.hidden
+        if y_host.numel() != h_host.numel():
+            raise C.B200MoeError("pipeline: input and output sizes differ")
+        with torch.cuda.device(self.layer.device):
+            C.check(C.lib.b200moe_pipeline_submit(self._handle, _ptr(h_host), _ptr(y_host), tokens,
+                                                  _stream()), "pipeline_submit")
+
+    def drain(self):
+        C.check(C.lib.b200moe_pipeline_drain(self._handle), "pipeline_drain")
+
+    def close(self):
+        if self._handle:
+            C.check(C.lib.b200moe_pipeline_destroy(self._handle), "pipeline_destroy")
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 _LAYERS: dict[int, PreparedLayer] = {}
 
 

@@ -211,31 +211,28 @@ class CudaBackend:
         return y
 
 
-class P2PExpertParallelMoeBlock(torch.nn.Module):
-    """The same layer with dispatch and combine as direct peer-to-peer stores into
-    symmetric buffers (`b200moe_ep_*`): no host synchronisation and no library
-    collective per call.  `max_tokens` bounds the tokens of the whole job per call
-    (it sizes the receive buffer for the worst routing: every token on this rank's
-    experts); `max_local_tokens` bounds this rank's own tokens."""
+class P2PExchange:
+    """The symmetric buffers of the peer-to-peer token exchange and its barrier
+    epoch counter.  One exchange serves any number of layers of the same hidden
+    size on this rank (a stack of MoE layers): the buffers are reused layer after
+    layer, the epochs keep counting.  `max_tokens` bounds the tokens of the whole
+    job per call (it sizes the receive buffer for the worst routing: every token
+    on this rank's experts); `max_local_tokens` bounds this rank's own tokens."""
 
-    def __init__(self, layer, expert_count: int, top_k: int, max_tokens: int, max_local_tokens: int,
-                 group=None, regime: int = 0):
-        super().__init__()
+    def __init__(self, hidden: int, expert_count: int, top_k: int, max_tokens: int, max_local_tokens: int,
+                 group=None, device=None):
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import _cabi as C
 
-        self.C = C
-        self.layer = layer
-        self.regime = regime
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         assert expert_count % self.world == 0 and self.world <= 16
-        self.expert_count, self.top_k = expert_count, top_k
+        self.expert_count, self.top_k, self.hidden = expert_count, top_k, hidden
         self.el = expert_count // self.world
-        self.dev = layer.device
-        d = layer.hidden
+        self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        d = hidden
         self.cap_rows = max_tokens * min(top_k, self.el)
         self.ret_rows = max_local_tokens * top_k
         self.max_segment = max_tokens
@@ -243,11 +240,11 @@ class P2PExpertParallelMoeBlock(torch.nn.Module):
         def up(n):
             return (n + 1023) // 1024 * 1024
 
-        self.off_counts = 0
-        self.off_flags = up(self.world * expert_count * 4)
-        self.off_recv = self.off_flags + 1024
-        self.off_ret = self.off_recv + up(self.cap_rows * d * 2)
-        total = self.off_ret + up(self.ret_rows * d * 2)
+        off_counts = 0
+        off_flags = up(self.world * expert_count * 4)
+        off_recv = off_flags + 1024
+        off_ret = off_recv + up(self.cap_rows * d * 2)
+        total = off_ret + up(self.ret_rows * d * 2)
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.dev)
         self.buf.zero_()
         self.hdl = symm_mem.rendezvous(self.buf, group=self.group)
@@ -257,63 +254,69 @@ class P2PExpertParallelMoeBlock(torch.nn.Module):
         ep = C.EpDesc()
         ep.world, ep.rank, ep.experts_local = self.world, self.rank, self.el
         for i, base in enumerate(ptrs):
-            ep.counts_all[i] = base + self.off_counts
-            ep.flags[i] = base + self.off_flags
-            ep.recv_x[i] = base + self.off_recv
-            ep.ret_y[i] = base + self.off_ret
+            ep.counts_all[i] = base + off_counts
+            ep.flags[i] = base + off_flags
+            ep.recv_x[i] = base + off_recv
+            ep.ret_y[i] = base + off_ret
         self.ep = ep
         self.epoch = 0
-        self.recv_x = self.buf[self.off_recv:self.off_recv + self.cap_rows * d * 2].view(torch.float16).view(self.cap_rows, d)
-        self.ret_y = self.buf[self.off_ret:self.off_ret + self.ret_rows * d * 2].view(torch.bfloat16).view(self.ret_rows, d)
-        self.seg2 = torch.zeros(self.el + 1, dtype=torch.int32, device=self.dev)
-        self.a = torch.empty(self.cap_rows, layer.ffn, dtype=torch.float16, device=self.dev)
+        self._workspace = None
+
+    def workspace(self, nbytes: int) -> torch.Tensor:
+        if self._workspace is None or self._workspace.numel() < nbytes:
+            self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.dev)
+        return self._workspace
+
+
+class P2PExpertParallelMoeBlock(torch.nn.Module):
+    """The same layer with dispatch and combine as direct peer-to-peer stores into
+    symmetric buffers: no host synchronisation and no library collective per
+    call, and the whole sequence is one C call (`b200moe_ep_layer_forward`).
+    Layers of a stack share one `P2PExchange` (and its workspace)."""
+
+    def __init__(self, layer, expert_count: int, top_k: int, max_tokens: int = 0, max_local_tokens: int = 0,
+                 group=None, regime: int = 0, exchange: Optional[P2PExchange] = None):
+        super().__init__()
+        from . import _cabi as C
+
+        self.C = C
+        self.layer = layer
+        self.regime = regime
+        self.x = exchange if exchange is not None else P2PExchange(
+            layer.hidden, expert_count, top_k, max_tokens, max_local_tokens, group, layer.device)
+        assert self.x.hidden == layer.hidden and self.x.expert_count == expert_count
+        self.group, self.world, self.rank = self.x.group, self.x.world, self.x.rank
+        self.expert_count, self.top_k = expert_count, top_k
+        self.dev = layer.device
+        # the layer descriptor of this rank's shard: local experts, global numbering
+        self.desc = C.LayerDesc.from_buffer_copy(layer.desc)
+        self.desc.experts = expert_count
+        self.desc.expert_begin = self.rank * self.x.el
         # load balance is steered by the rows expected under uniform routing, the
         # buffers are sized for the worst case
-        expected = max(1, max_tokens * top_k // self.world)
-        self.ks = C.lib.b200moe_down_ksplit(ctypes.byref(layer.down.desc), expected,
-                                            self.max_segment, regime)
-        self.dpart = torch.empty(self.ks, self.cap_rows, d, dtype=torch.float32, device=self.dev)
-        self.backend = CudaBackend(layer, regime)
-        self.launches_per_step = 12
+        expected = max(1, self.x.max_segment * top_k // self.world)
+        self.ks = C.lib.b200moe_down_ksplit(ctypes.byref(layer.down.desc), expected, self.x.max_segment, regime)
+        self.backend = CudaBackend(layer, regime)  # carries the profile switch for benchmarks
+        self.launches_per_step = 11
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        C, L, b = self.C, self.layer, self.backend
-        p, st = b._p, b._st()
+        C, x = self.C, self.x
         shape = h.shape
-        x = h.reshape(-1, shape[-1]).contiguous()
-        tokens = x.shape[0]
-        pairs = tokens * self.top_k
-        assert pairs <= self.ret_rows, "more local tokens than the block was sized for"
-        ep = ctypes.byref(self.ep)
-        xn, experts, gates = b.route(x)
-        counts, seg, perm, inv = b.plan(experts.reshape(-1), self.expert_count, 0)
-        C.check(C.lib.b200moe_ep_publish_counts(ep, p(counts), st), "ep_publish_counts")
-        C.check(C.lib.b200moe_ep_barrier(ep, self.epoch + 1, p(self.seg2), st), "ep_barrier")
-        kp_in = C.lib.b200moe_kperm(L.gate.layout, self.regime, self.max_segment)
-        C.check(C.lib.b200moe_ep_dispatch(ep, p(xn), p(experts), p(perm), p(seg), pairs, self.top_k,
-                                          L.hidden, kp_in, self.cap_rows, st), "ep_dispatch")
-        C.check(C.lib.b200moe_ep_barrier(ep, self.epoch + 2, None, st), "ep_barrier")
-        prof = b.profile
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if prof else None
-        if ev:
-            ev[0].record()
-        kp = C.lib.b200moe_kperm(L.down.layout, self.regime, self.max_segment)
-        C.check(C.lib.b200moe_gate_up(p(self.recv_x), p(self.seg2), self.cap_rows, self.max_segment,
-                                      ctypes.byref(L.gate.desc), ctypes.byref(L.up.desc),
-                                      L.desc.activation, self.regime, kp, p(self.a), st), "gate_up")
-        if ev:
-            ev[1].record()
-        C.check(C.lib.b200moe_down(p(self.a), p(self.seg2), self.cap_rows, self.max_segment,
-                                   ctypes.byref(L.down.desc), self.regime, self.ks, p(self.dpart), st),
-                "down")
-        if ev:
-            ev[2].record()
-            b.timings.append((ev, -1))  # rows received are only known on the device
-        C.check(C.lib.b200moe_ep_return(ep, p(self.dpart), self.ks, self.cap_rows, p(self.seg2),
-                                        L.hidden, self.ret_rows, st), "ep_return")
-        C.check(C.lib.b200moe_ep_barrier(ep, self.epoch + 3, None, st), "ep_barrier")
-        self.epoch += 3
-        y = b.combine(self.ret_y[:pairs], inv, gates, x)
+        xin = h.reshape(-1, shape[-1]).contiguous()
+        tokens = xin.shape[0]
+        if xin.dtype not in (torch.float32, torch.bfloat16):
+            raise C.B200MoeError(f"activations must be fp32 or bf16, got {xin.dtype}")
+        dt = C.DT_F32 if xin.dtype == torch.float32 else C.DT_BF16
+        y = torch.empty_like(xin)
+        nbytes = C.lib.b200moe_ep_workspace_bytes(ctypes.byref(self.desc), tokens, x.cap_rows, self.ks)
+        ws = x.workspace(nbytes)
+        p = CudaBackend._p
+        with torch.cuda.device(self.dev):
+            C.check(C.lib.b200moe_ep_layer_forward(
+                ctypes.byref(self.desc), ctypes.byref(x.ep), p(xin), p(y), dt, tokens, self.regime,
+                x.cap_rows, x.ret_rows, x.max_segment, self.ks, x.epoch, p(ws), ws.numel(),
+                ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)), "ep_layer_forward")
+        x.epoch += 3
         return y.reshape(shape)
 
 
@@ -335,22 +338,22 @@ def shard_theta(theta, rank: int):
 
 def build_block(theta_local, expert_count: int, top_k: int, rms_epsilon: float, activation: str,
                 group=None, regime: str = "auto", transport: str = "nccl", max_tokens: int = 0,
-                max_local_tokens: int = 0):
+                max_local_tokens: int = 0, exchange: Optional[P2PExchange] = None):
     """theta_local holds this rank's expert shard ([E/W, ...] tensors) and the
     replicated router / norm weights, all on this rank's GPU.  transport "nccl":
     all-to-all collectives; "p2p": direct stores into symmetric buffers (needs
-    max_tokens / max_local_tokens to size them)."""
+    max_tokens / max_local_tokens to size them, or an existing `exchange`)."""
     from . import moe
 
     layer = moe.PreparedLayer(theta_local, expert_count, top_k, rms_epsilon, activation)
     if transport == "p2p":
         return P2PExpertParallelMoeBlock(layer, expert_count, top_k, max_tokens, max_local_tokens,
-                                         group, moe.REGIMES[regime])
+                                         group, moe.REGIMES[regime], exchange)
     return ExpertParallelMoeBlock(CudaBackend(layer, moe.REGIMES[regime]), expert_count, top_k, group)
 
 
 def build_from_case(case, group=None, regime: str = "auto", transport: str = "nccl",
-                    max_local_tokens: int = 0):
+                    max_local_tokens: int = 0, exchange: Optional[P2PExchange] = None):
     """Benchmark/test helper: slice a synthetic case's expert planes for this rank."""
     from . import types as T
     from .synthetic import DENSE, Q8_0
@@ -386,4 +389,4 @@ def build_from_case(case, group=None, regime: str = "auto", transport: str = "nc
         tree["layer_output_norm"] = {"weight": T.DefaultPrimitiveTensor(data=case.out_norm_w.to(dev))}
     tokens = case.h.shape[1]
     return build_block(T.Theta(tree), s.experts, s.top_k, s.eps, s.activation, group, regime,
-                       transport, tokens, max_local_tokens or -(-tokens // world))
+                       transport, tokens, max_local_tokens or -(-tokens // world), exchange)

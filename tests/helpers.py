@@ -52,6 +52,10 @@ def dense_weight(kind, planes):
     """The dense tensor the reference's eager kernels see for a weight."""
     if kind == syn.DENSE:
         return planes["w"]
+    if planes["qs"].numel() > (1 << 26):
+        # full-size layers: the multi-threaded restatement (bit-equal to the numpy
+        # one, tests/test_oracle.py), seconds instead of a minute
+        return orc.dequant_torch(kind, planes)
     return torch.from_numpy(orc.dequant(kind, np_planes(planes)))
 
 

@@ -114,6 +114,37 @@ def test_router_indices_bit_exact_and_gates(M, name):
     assert np.abs(gates.cpu().numpy() - g["gate"]).max() < GATE_TOL
 
 
+@pytest.mark.parametrize("name", ["small_q8", "small_top4", "small_grok"])
+def test_prefill_router_equals_the_per_warp_router(M, name):
+    """From 1024 tokens the router keeps its weights in shared memory; per token
+    it performs the operations of the one-warp-per-token kernel in the same
+    order, so routing a batch at once or in slices of 600 tokens gives the same
+    bits."""
+    from shark_platform_b200 import _cabi as C
+
+    tokens = 1500
+    case = syn.make_case(syn.CASES[name], tokens=tokens)
+    layer = b200_block(case).layer
+    h = device_input(case).reshape(tokens, -1).contiguous()
+    dt = C.DT_BF16 if h.dtype == torch.bfloat16 else C.DT_F32
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def route(rows):
+        n = rows.shape[0]
+        xn = torch.empty(n, layer.hidden, dtype=torch.float16, device="cuda")
+        ex = torch.empty(n, layer.top_k, dtype=torch.int32, device="cuda")
+        gt = torch.empty(n, layer.top_k, dtype=torch.float32, device="cuda")
+        C.check(C.lib.b200moe_router(p(rows), dt, n, ctypes.byref(layer.desc), p(xn), p(ex), p(gt), st))
+        return xn, ex, gt
+
+    whole = route(h)
+    parts = [route(h[i:i + 600].contiguous()) for i in range(0, tokens, 600)]
+    for i in range(3):
+        assert torch.equal(whole[i], torch.cat([pt[i] for pt in parts]))
+    assert M.device_status() == 0
+
+
 def _check_plan(M, experts, E, begin=0, local=None):
     local = E if local is None else local
     plan = M.route_plan(experts.cuda(), local, begin)
@@ -582,3 +613,29 @@ def test_patch_moe_blocks_swaps_every_block(M):
     for blk, case in zip(model.moe_blocks, cases):
         want = b200_block(case)(device_input(case))
         assert torch.equal(blk(device_input(case)), want)
+
+
+# ------------------------------------------------ host-buffer pipeline
+@pytest.mark.parametrize("depth", [1, 2, 3])
+def test_host_pipeline_equals_device_calls(M, depth):
+    """Batches in pinned host memory streamed through the layer with `depth`
+    steps in flight: every step's output equals the device-resident call on the
+    same input, whatever the overlap between steps."""
+    case = syn.make_case(syn.CASES["small_q8"], tokens=300)
+    blk = b200_block(case)
+    gen = torch.Generator().manual_seed(8)
+    steps = 7
+    hs = [torch.randn(300 - 10 * i, case.spec.hidden, generator=gen).to(torch.bfloat16).pin_memory()
+          for i in range(steps)]
+    ys = [torch.full_like(h, float("nan")).pin_memory() for h in hs]
+    pipe = M.HostPipeline(blk.layer, 300, torch.bfloat16, depth=depth)
+    for h, y in zip(hs, ys):
+        pipe.submit(h, y)
+    pipe.drain()
+    for h, y in zip(hs, ys):
+        want = blk.layer.forward(h.cuda())
+        assert torch.equal(y.cuda(), want)
+    with pytest.raises(M.C.B200MoeError):
+        pipe.submit(torch.zeros(301, case.spec.hidden, dtype=torch.bfloat16), torch.zeros(301, case.spec.hidden, dtype=torch.bfloat16))
+    pipe.close()
+    assert M.device_status() == 0

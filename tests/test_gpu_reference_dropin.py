@@ -59,8 +59,8 @@ def test_reference_moeblock_runs_on_quantized_experts_through_the_plugin(name):
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device")
     import_sharktank()
-    import sharktank.ops as st_ops
     from sharktank.layers.mixture_of_experts_block import MoeBlock
+    from sharktank.ops import _registry as st_registry
 
     from shark_platform_b200 import moe, plugin
 
@@ -85,15 +85,15 @@ def test_reference_moeblock_runs_on_quantized_experts_through_the_plugin(name):
     # dispatch, as the reference's registry records it
     xn = orc.rms_norm(case.h, p.norm_w, p.eps).view(-1, s.hidden)
     gate, idx, _ = orc.router(xn, p.router_w, p.router_b, p.top_k)
-    st_ops._test_enable_last_op_dispatch(True)
+    st_registry._test_enable_last_op_dispatch(True)
     try:
         gathered = block.experts.ffn_gate[idx.cuda(), :, :]
-        assert st_ops._test_get_last_op_dispatch() is moe.get_index_quantized
+        assert st_registry._test_get_last_op_dispatch() is moe.get_index_quantized
         assert isinstance(gathered, moe.GatheredExperts)
         out = block.experts.pre_matmul_gather(xn.cuda(), block.experts.ffn_up, idx.cuda())
-        assert st_ops._test_get_last_op_dispatch() is moe.einsum_2args_gathered
+        assert st_registry._test_get_last_op_dispatch() is moe.einsum_2args_gathered
     finally:
-        st_ops._test_enable_last_op_dispatch(False)
+        st_registry._test_enable_last_op_dispatch(False)
     want_up = torch.einsum("mk,menk->men", xn, p.w_up[idx].float())
     assert orc.rel_l2(out.cpu(), want_up) < 5e-3
 
