@@ -342,13 +342,21 @@ def measure_layer(C, moe, syn, block, h, spec, args, peaks, sampler=None, cold=T
         y = step()
     torch.cuda.synchronize()
     moe.device_status()
+    if sampler is not None:
+        sampler.start()
     soak_steps = soak(step)
     ms_total = event_ms(step, args.steps)
     ms_step = ms_total / args.steps
     moe.device_status()
     stage = stage_times(C, step, args.steps)
+    clocks = None
+    if sampler is not None:
+        soak(step, 0.25)  # the sampler's period is 100 ms: a few more samples of the same load
+        clocks = sampler.stop()
+        clocks["window"] = (f"{SOAK_S} s of the same steps before the timed region, the timed region, the "
+                            "stage-event pass and 0.25 s more of the same steps")
     y = step()
-    out = {"value": tokens / (ms_step * 1e-3), "ms_per_step": ms_step, "stage_ms": stage,
+    out = {"value": tokens / (ms_step * 1e-3), "ms_per_step": ms_step, "stage_ms": stage, "clocks": clocks,
            "soak_steps_before_timing": soak_steps,
            "roofline": roofline_single(syn, spec, tokens, stage, peaks)}
     flops = syn.layer_flops(tokens, spec.top_k, spec.hidden, spec.ffn)
@@ -461,20 +469,13 @@ def main():
         h = syn.case_input(case, dev).reshape(tokens, spec.hidden).contiguous()
         fused = C.lib.b200moe_front_supported(tokens, ctypes.byref(block.layer.desc))
         launches_per_step = 4 if fused else 6
-        sampler.start()
-        time.sleep(0.3)
-        m = measure_layer(C, moe, syn, block, h, spec, args, peaks)
-        clocks = sampler.stop()
-        clocks["window"] = (f"{SOAK_S} s of the same steps before the timed region, the timed region, the "
-                            "stage-event pass and the host-buffer passes")
+        m = measure_layer(C, moe, syn, block, h, spec, args, peaks, sampler)
+        clocks = m["clocks"]
         if args.workload == "prefill4096" and not args.no_secondary:
             # the other headline target, on the same layer in the same run
             h32 = h[:32].contiguous()
-            s2 = ClockSampler(local_rank)
-            s2.start()
-            time.sleep(0.3)
-            m2 = measure_layer(C, moe, syn, block, h32, spec, args, peaks)
-            c2 = s2.stop()
+            m2 = measure_layer(C, moe, syn, block, h32, spec, args, peaks, ClockSampler(local_rank))
+            c2 = m2["clocks"]
             secondary = {"decode32": {
                 "config": {"workload": "decode32", "tokens": 32, "note": "first 32 tokens of the same batch, same layer"},
                 "value": m2["value"], "unit": "tokens/s", "ms_per_step": m2["ms_per_step"],

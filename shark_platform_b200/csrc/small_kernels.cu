@@ -295,6 +295,130 @@ router_smem_kernel(const T* __restrict__ h, int tokens, int d, int E, int k, flo
   }
 }
 
+// The same kernel for bf16 activations with the token's row held in registers:
+// all of a row's loads are issued at once (one memory latency per token instead
+// of one per loop iteration) and, with PREFETCH, the next token's row is already
+// in flight while this one is being routed.  Arithmetic and its order are
+// unchanged.  MAXIT >= hidden / 256 (16: hidden up to 4096).
+template <int MAXIT, bool PREFETCH>
+__global__ void __launch_bounds__(RS_WARPS * 32)
+router_smem_bf16_kernel(const __nv_bfloat16* __restrict__ h, int tokens, int d, int E, int k, float eps,
+                        const float* __restrict__ norm_w, const float* __restrict__ rw,
+                        const float* __restrict__ rb, __half* __restrict__ xn_out,
+                        int32_t* __restrict__ experts_out, float* __restrict__ gates_out) {
+  extern __shared__ float s_dyn[];
+  float* s_w = s_dyn;
+  float* s_n = s_dyn + static_cast<size_t>(E) * d;
+  float* s_logit = s_n + d;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nit = d >> 8;
+  const int stride = gridDim.x * RS_WARPS;
+  int t = blockIdx.x * RS_WARPS + warp;
+  uint4 cur[MAXIT], nxt[PREFETCH ? MAXIT : 1];
+#define B200_LOAD_ROW(dst, tok)                                                              \
+  {                                                                                          \
+    const uint4* row_ = reinterpret_cast<const uint4*>(h + static_cast<size_t>(tok) * d) + lane; \
+    _Pragma("unroll") for (int it = 0; it < MAXIT; ++it) if (it < nit) dst[it] = row_[it * 32];  \
+  }
+  if (t < tokens) B200_LOAD_ROW(cur, t);  // in flight while the weights are staged
+  auto slot = [](int j) { return (((j >> 8) * 2 + ((j >> 2) & 1)) * 32 + ((j >> 3) & 31)) * 4 + (j & 3); };
+  for (int idx = threadIdx.x * 4; idx < E * d; idx += RS_WARPS * 32 * 4) {
+    const int e = idx / d, j = idx - e * d;
+    *reinterpret_cast<float4*>(s_w + static_cast<size_t>(e) * d + slot(j)) =
+        *reinterpret_cast<const float4*>(rw + idx);
+  }
+  for (int j = threadIdx.x * 4; j < d; j += RS_WARPS * 32 * 4)
+    *reinterpret_cast<float4*>(s_n + slot(j)) = *reinterpret_cast<const float4*>(norm_w + j);
+  __syncthreads();
+
+  auto unpack = [](const uint4& raw, float (&v)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  };
+
+  for (; t < tokens; t += stride) {
+    if constexpr (PREFETCH) {
+      if (t + stride < tokens) B200_LOAD_ROW(nxt, t + stride);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < MAXIT; ++it) {
+      if (it < nit) {
+        float v[8];
+        unpack(cur[it], v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = 1.0f / sqrtf(ss / static_cast<float>(d) + eps);
+
+    for (int e0 = 0; e0 < E; e0 += 8) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int it = 0; it < MAXIT; ++it) {
+        if (it < nit) {
+          float v[8], w[8];
+          unpack(cur[it], v);
+          const int base = (it * 2 * 32 + lane) * 4;
+          {
+            const float4 a = *reinterpret_cast<const float4*>(s_n + base);
+            const float4 b = *reinterpret_cast<const float4*>(s_n + base + 128);
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+            w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = w[i] * (v[i] * rstd);
+          if (e0 == 0) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              packed[i] = h2_as_u32(__halves2half2(to_half_sat(v[2 * i]), to_half_sat(v[2 * i + 1])));
+            *reinterpret_cast<uint4*>(xn_out + static_cast<size_t>(t) * d + it * 256 + lane * 8) =
+                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            if (e0 + e < E) {
+              const float* wr = s_w + static_cast<size_t>(e0 + e) * d + base;
+              const float4 a = *reinterpret_cast<const float4*>(wr);
+              const float4 b = *reinterpret_cast<const float4*>(wr + 128);
+              const float r[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[e] = fmaf(v[i], r[i], acc[e]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+        if (lane == 0 && e0 + e < E)
+          s_logit[warp * MAX_EXPERTS + e0 + e] = acc[e] + (rb ? rb[e0 + e] : 0.f);
+      }
+    }
+    __syncwarp();
+    router_select(s_logit + warp * MAX_EXPERTS, lane, E, k, experts_out + static_cast<size_t>(t) * k,
+                  gates_out + static_cast<size_t>(t) * k);
+    __syncwarp();
+    if constexpr (PREFETCH) {
+#pragma unroll
+      for (int it = 0; it < MAXIT; ++it) cur[it] = nxt[it];
+    } else {
+      if (t + stride < tokens) B200_LOAD_ROW(cur, t + stride);
+    }
+  }
+#undef B200_LOAD_ROW
+}
+
 // One CTA per token: used for small token counts (decode), where a warp per
 // token leaves most of the GPU idle.  The row stays in registers between the
 // two passes (hidden <= 8192).
@@ -635,29 +759,29 @@ int launch_router(const void* h, int h_dtype, int tokens, const b200moe_layer_t*
   const size_t rs_smem = (static_cast<size_t>(L->experts) * L->hidden + L->hidden +
                           RS_WARPS * MAX_EXPERTS) * sizeof(float);
   if (tokens >= 1024 && rs_smem <= 227 * 1024) {
-    static bool configured[16][2] = {};
+    const int ctas = min(sm_count(), (tokens + RS_WARPS - 1) / RS_WARPS);
+    const void* fn;
+    int which;
+    if (h_dtype == B200MOE_DT_F32) {
+      fn = reinterpret_cast<const void*>(&router_smem_kernel<float>); which = 0;
+    } else if (L->hidden <= 4096) {
+      fn = reinterpret_cast<const void*>(&router_smem_bf16_kernel<16, true>); which = 1;
+    } else {  // longer rows do not fit the register file twice over: two passes over global memory
+      fn = reinterpret_cast<const void*>(&router_smem_kernel<__nv_bfloat16>); which = 3;
+    }
+    static bool configured[16][4] = {};
     int dev = 0;
     B200_CHECK_CUDA(cudaGetDevice(&dev));
-    const int ti = h_dtype == B200MOE_DT_F32 ? 0 : 1;
-    if (dev < 16 && !configured[dev][ti]) {
-      B200_CHECK_CUDA(cudaFuncSetAttribute(
-          ti == 0 ? reinterpret_cast<const void*>(&router_smem_kernel<float>)
-                  : reinterpret_cast<const void*>(&router_smem_kernel<__nv_bfloat16>),
-          cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-      configured[dev][ti] = true;
+    if (dev < 16 && !configured[dev][which]) {
+      B200_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+      configured[dev][which] = true;
     }
-    const int ctas = min(sm_count(), (tokens + RS_WARPS - 1) / RS_WARPS);
-    if (h_dtype == B200MOE_DT_F32)
-      router_smem_kernel<float><<<ctas, RS_WARPS * 32, rs_smem, st>>>(
-          static_cast<const float*>(h), tokens, L->hidden, L->experts, L->top_k, L->rms_epsilon,
-          L->ffn_norm_weight, L->router_weight, L->router_bias, static_cast<__half*>(xn), experts,
-          gates);
-    else
-      router_smem_kernel<__nv_bfloat16><<<ctas, RS_WARPS * 32, rs_smem, st>>>(
-          static_cast<const __nv_bfloat16*>(h), tokens, L->hidden, L->experts, L->top_k,
-          L->rms_epsilon, L->ffn_norm_weight, L->router_weight, L->router_bias,
-          static_cast<__half*>(xn), experts, gates);
-    B200_CHECK_CUDA(cudaGetLastError());
+    int d_ = L->hidden, E_ = L->experts, k_ = L->top_k;
+    float eps_ = L->rms_epsilon;
+    const float *nw = L->ffn_norm_weight, *rwp = L->router_weight, *rbp = L->router_bias;
+    __half* xnp = static_cast<__half*>(xn);
+    void* args[] = {&h, &tokens, &d_, &E_, &k_, &eps_, &nw, &rwp, &rbp, &xnp, &experts, &gates};
+    B200_CHECK_CUDA(cudaLaunchKernel(fn, dim3(ctas), dim3(RS_WARPS * 32), args, rs_smem, st));
     return B200MOE_OK;
   }
   dim3 grid((tokens + ROUTER_WARPS - 1) / ROUTER_WARPS), block(ROUTER_WARPS * 32);

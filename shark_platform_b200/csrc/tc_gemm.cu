@@ -229,11 +229,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       mbar_init(sempty + 8u * s, TC_DQ_WARPS);
     }
     for (int s = 0; s < TC_ASLOTS; ++s) {
-      mbar_init(a_ready + 8u * s, 256);
+      mbar_init(a_ready + 8u * s, TC_DQ_WARPS / 2);  // one arrival per warp of the group that fills the slot
       mbar_init(a_free + 8u * s, 1);
     }
     mbar_init(acc_full_bar, 1);
-    mbar_init(acc_empty_bar, TC_DQ_WARPS * 32);
+    mbar_init(acc_empty_bar, TC_DQ_WARPS);  // one arrival per dequant warp
     fence_mbar_init();
     int run = 0;
     for (int e = 0; e < args.E; ++e) {
@@ -467,7 +467,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           tmem_st32(tmem + lane_addr + TC_COL_A + as * 64 + set * 32, v);
           tmem_wait_st();
           tc_fence_before();
-          mbar_arrive(a_ready + 8u * as);
+          // one arrival per warp: 256 arrivals per stage on one barrier word
+          // serialise in shared memory
+          __syncwarp();
+          if (lane == 0) mbar_arrive(a_ready + 8u * as);
         }
       }
       if (!ok) break;
@@ -500,7 +503,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         }
       }
       tc_fence_before();
-      mbar_arrive(acc_empty_bar);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar);
     }
   }
 

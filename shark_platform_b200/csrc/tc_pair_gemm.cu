@@ -271,11 +271,11 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
       mbar_init(sempty + 8u * s, TP_DQ_WARPS);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(a_ready + 8u * s, 2 * 256);   // used in the leader only: both CTAs' dequant threads
+      mbar_init(a_ready + 8u * s, TP_DQ_WARPS);  // leader only: one arrival per warp of the filling group, both CTAs
       mbar_init(a_free + 8u * s, 1);
     }
     mbar_init(acc_full_bar, 1);
-    mbar_init(acc_empty_bar, 2 * TP_DQ_WARPS * 32);  // leader only
+    mbar_init(acc_empty_bar, 2 * TP_DQ_WARPS);  // leader only: one arrival per dequant warp of both CTAs
     fence_mbar_init();
     int run = 0;
     for (int e = 0; e < args.E; ++e) {
@@ -516,7 +516,10 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
           tp_tmem_st32(tmem + lane_addr + TP_COL_A + as * 64 + set * 32, v);
           tp_wait_st();
           tp_fence_before();
-          mbar_arrive_cluster(a_ready_leader + 8u * as);
+          // one arrival per warp: an arrival on the leader's barrier from the
+          // peer CTA is a transaction over the SM-to-SM network
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(a_ready_leader + 8u * as);
         }
       }
       if (!ok) break;
@@ -549,7 +552,8 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
         }
       }
       tp_fence_before();
-      mbar_arrive_cluster(acc_empty_leader);
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
     }
   }
 
