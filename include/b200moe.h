@@ -360,6 +360,19 @@ int b200moe_pipeline_destroy(b200moe_pipeline_t* p);
 int b200moe_profile_enable(int on);
 int b200moe_profile_read(float* ms_out, int32_t* calls_out);
 
+/* Diagnostic (no reference counterpart): while enabled, every launch of the
+ * CTA-pair tensor kernel records clock64 time stamps of its first CTA pair's
+ * warp roles for the first 256 stages.  b200moe_trace_read synchronises the
+ * device and copies the last launch's record: int64 [2 CTAs][5 roles][256
+ * stages][8 points]; roles: 0 weight producer (0 before / 1 after its wait for
+ * a free slot), 1 token producer (0 / 1 likewise), 2 MMA issuer (0 start, 1
+ * tokens arrived, 2 A operand ready, 3 MMAs issued), 3 and 4 the two dequant
+ * groups (0 start, 1 weights arrived, 2 dequantised, 3 A slot free, 4 stored).
+ * clock64 counts per SM: the two CTAs' stamps are not on one time base.
+ * count = number of int64 values `out` can hold (at least 20480). */
+int b200moe_trace_enable(int on);
+int b200moe_trace_read(int64_t* out, size_t count);
+
 #ifdef __cplusplus
 }
 #endif

@@ -602,6 +602,13 @@ int b200moe_ep_layer_forward(const b200moe_layer_t* L, const b200moe_ep_t* ep, c
   return B200MOE_OK;
 }
 
+int b200moe_trace_enable(int on) { return pair_trace_enable(on != 0); }
+
+int b200moe_trace_read(int64_t* out, size_t count) {
+  static_assert(sizeof(int64_t) == sizeof(long long), "trace element size");
+  return pair_trace_read(reinterpret_cast<long long*>(out), count);
+}
+
 int b200moe_profile_enable(int on) {
   if (on && !g_prof.created) {
     for (int c = 0; c < PROF_CALLS; ++c)

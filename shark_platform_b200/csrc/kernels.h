@@ -60,4 +60,7 @@ int launch_tc_pair_gate_up(const void* xs, const int32_t* seg, int pairs, int to
 int launch_tc_pair_down(const void* a_in, const int32_t* seg, int pairs, int tok_tile,
                         const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st);
 
+int pair_trace_enable(bool on);
+int pair_trace_read(long long* out, size_t count);
+
 }  // namespace b200moe

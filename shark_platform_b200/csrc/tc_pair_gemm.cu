@@ -76,7 +76,20 @@ struct TpArgs {
   const uint8_t* st0;
   const uint8_t* st1;
   long long total_rows;
+  long long* trace;  // NULL, or [2 CTAs][TR_ROLES][TR_STAGES][TR_POINTS] clock64 stamps of CTA pair 0
 };
+
+// Diagnostic time stamps (b200moe_trace_*): the first TR_STAGES stages of the
+// first CTA pair, one row per warp role.  clock64 is per SM: stamps of the two
+// CTAs are not on one time base.
+constexpr int TR_ROLES = 5, TR_STAGES = 256, TR_POINTS = 8;
+__device__ long long g_tp_trace[2 * TR_ROLES * TR_STAGES * TR_POINTS];
+bool g_tp_trace_on = false;
+
+__device__ __forceinline__ void tr_mark(long long* trace, uint32_t rank, int role, uint32_t stage, int point) {
+  if (trace != nullptr && stage < TR_STAGES)
+    trace[((rank * TR_ROLES + role) * TR_STAGES + stage) * TR_POINTS + point] = clock64();
+}
 
 // ---- cluster helpers ---------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -256,6 +269,7 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
   const uint32_t rank = cluster_ctarank();       // 0 = leader
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  long long* const tr = pair == 0 ? args.trace : nullptr;
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < TP_WSLOTS; ++s) {
@@ -364,7 +378,9 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
           }
           const uint32_t wi = n >> 1;
           const int ws = wi % TP_WSLOTS;
+          tr_mark(tr, rank, 0, n, 0);
           if (!mbar_wait(wempty + 8u * ws, ((wi / TP_WSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          tr_mark(tr, rank, 0, n, 1);
           fence_proxy_async_smem();
           const uint32_t wdst = smem_base + ws * TP_WSLOT;
           const uint32_t wb = wfull + 8u * ws;
@@ -396,7 +412,9 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
         for (int st = 0; st < stages_per_tile; ++st, ++n) {
           const int xs = n % TP_XSLOTS;
           // freed in both CTAs by the leader's commit
+          tr_mark(tr, rank, 1, n, 0);
           if (!mbar_wait(xempty + 8u * xs, ((n / TP_XSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          tr_mark(tr, rank, 1, n, 1);
           if (leader) mbar_expect_tx(xfull + 8u * xs, 2 * half_bytes);
           tma_load_2d_pair(x_base + xs * TP_XSLOT, tx, ((nt >> 16) * stages_per_tile + st) * TP_KT * 2,
                            my_row0, xfull_leader + 8u * xs);
@@ -420,11 +438,11 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
         for (int st = 0; st < stages_per_tile; ++st, ++n) {
           const int xs = n % TP_XSLOTS;
           const int as = n & 1;
-          if (!mbar_wait(xfull + 8u * xs, (n / TP_XSLOTS) & 1u, abort_flag, args.status) ||
-              !mbar_wait_cluster(a_ready + 8u * as, (n >> 1) & 1u, abort_flag, args.status)) {
-            ok = false;
-            break;
-          }
+          tr_mark(tr, rank, 2, n, 0);
+          if (!mbar_wait(xfull + 8u * xs, (n / TP_XSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
+          tr_mark(tr, rank, 2, n, 1);
+          if (!mbar_wait_cluster(a_ready + 8u * as, (n >> 1) & 1u, abort_flag, args.status)) { ok = false; break; }
+          tr_mark(tr, rank, 2, n, 2);
           tp_fence_after();
           const uint64_t bdesc = tp_smem_desc_sw128(x_base + xs * TP_XSLOT);
 #pragma unroll
@@ -437,6 +455,7 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
           }
           tp_commit_both(xempty + 8u * xs);
           tp_commit_both(a_free + 8u * as);
+          tr_mark(tr, rank, 2, n, 3);
         }
         if (ok) tp_commit_both(acc_full_bar);
       }
@@ -474,7 +493,10 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
           const uint32_t wi = n >> 1;
           const int ws = wi % TP_WSLOTS;
           const int as = n & 1;
+          long long* const trd = (wq == 0 && set == 0 && lane == 0) ? tr : nullptr;
+          tr_mark(trd, rank, 3 + grp, n, 0);
           if (!mbar_wait_warp(wfull + 8u * ws, (wi / TP_WSLOTS) & 1u, abort_flag, args.status)) { ok = false; break; }
+          tr_mark(trd, rank, 3 + grp, n, 1);
           uint32_t v[32];
           if constexpr (Q4) {
             const uint32_t wrow = smem_base + ws * TP_WSLOT + set * TP_WSET + row * 64;
@@ -511,11 +533,14 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                 dequant_q8x4(q[c][j], c < 2 ? s_lo : s_hi, v[c * 8 + 2 * j], v[c * 8 + 2 * j + 1]);
           }
           // this CTA's A slot is free once the pair's MMAs of stage n-2 are done
+          tr_mark(trd, rank, 3 + grp, n, 2);
           if (!mbar_wait_warp(a_free + 8u * as, ((n >> 1) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          tr_mark(trd, rank, 3 + grp, n, 3);
           tp_fence_after();
           tp_tmem_st32(tmem + lane_addr + TP_COL_A + as * 64 + set * 32, v);
           tp_wait_st();
           tp_fence_before();
+          tr_mark(trd, rank, 3 + grp, n, 4);
           // one arrival per warp: an arrival on the leader's barrier from the
           // peer CTA is a transaction over the SM-to-SM network
           __syncwarp();
@@ -570,8 +595,16 @@ tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
 }
 
 template <int LAYOUT, int NMAT>
-int tp_launch(const CUtensorMap* maps, const TpArgs& a, cudaStream_t st) {
+int tp_launch(const CUtensorMap* maps, const TpArgs& a_in, cudaStream_t st) {
   auto kern = tc_pair_gemm_kernel<LAYOUT, NMAT>;
+  TpArgs a = a_in;
+  a.trace = nullptr;
+  if (g_tp_trace_on) {
+    void* p = nullptr;
+    B200_CHECK_CUDA(cudaGetSymbolAddress(&p, g_tp_trace));
+    B200_CHECK_CUDA(cudaMemsetAsync(p, 0, sizeof(long long) * 2 * TR_ROLES * TR_STAGES * TR_POINTS, st));
+    a.trace = static_cast<long long*>(p);
+  }
   static bool configured[16] = {};
   int dev = 0;
   B200_CHECK_CUDA(cudaGetDevice(&dev));
@@ -605,6 +638,19 @@ int tp_weight_map(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts) {
 }
 
 }  // namespace
+
+int pair_trace_enable(bool on) {
+  g_tp_trace_on = on;
+  return B200MOE_OK;
+}
+
+int pair_trace_read(long long* out, size_t count) {
+  const size_t n = static_cast<size_t>(2) * TR_ROLES * TR_STAGES * TR_POINTS;
+  B200_REQUIRE(out != nullptr && count >= n, "trace_read: the buffer must hold %zu values", n);
+  B200_CHECK_CUDA(cudaDeviceSynchronize());
+  B200_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_tp_trace, sizeof(long long) * n));
+  return B200MOE_OK;
+}
 
 // The pair kernel needs an even number of row tiles per expert.
 bool tc_pair_supported_gate_up(const b200moe_weight_t* gate) {

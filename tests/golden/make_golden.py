@@ -9,6 +9,7 @@ Writes:
   formats.npz      packed Q8_0 / Q4_K blocks, the planes the reference's
                    `unpack()` produces and its `dequant()` values; outputs of
                    the bit-unpack helpers on random bytes
+  moe_bf16act.npz  sharktank's MoeBlock on bf16 activations (its bf16 router path)
   moe_<case>.npz   outputs of sharktank's MoeBlock for the small seeded cases
                    of shark_platform_b200.synthetic (quantized weights go
                    through `layout.dequant()` -> DefaultPrimitiveTensor, the
@@ -154,6 +155,43 @@ def main():
             digest=np.array(digest(case)),
         )
         print(f"moe_{name}.npz written  |y|={float(y.abs().mean()):.4f}")
+
+    # ---------------- bf16 activations through the reference ----------------
+    # With bf16 `h` the reference rounds the normalised row to bf16
+    # (layers/norm.py:39-41), computes the router logits in bf16 (the weight is
+    # cast to the input dtype, ops/default_impls.py:332-333) and casts the expert
+    # weights to bf16 as well (:351).  The CUDA path keeps norm, logits and gates
+    # in fp32; this fixture measures how far the two routings are apart.
+    spec = syn.CaseSpec("bf16act", 512, 256, 512, kind=syn.Q8_0, norm_weight="perturbed", seed=21)
+    case = syn.make_case(spec)
+    e, f, d = spec.experts, spec.ffn, spec.hidden
+    tree = {
+        "ffn_gate_inp": {"weight": DefaultPrimitiveTensor(data=case.router_w)},
+        "ffn_norm": {"weight": DefaultPrimitiveTensor(data=case.norm_w)},
+        "ffn_gate_exps": {"weight": ref_weight(spec.kind, case.gate, [e, f, d])},
+        "ffn_up_exps": {"weight": ref_weight(spec.kind, case.up, [e, f, d])},
+        "ffn_down_exps": {"weight": ref_weight(spec.kind, case.down, [e, d, f])},
+    }
+    block = MoeBlock(Theta(tree), e, spec.top_k, spec.eps, moe_activation=F.silu)
+    captured = {}
+    orig = block.experts.forward
+
+    def spy16(h, experts, expert_gate):
+        captured["experts"] = experts.clone()
+        captured["gate"] = expert_gate.clone()
+        return orig(h, experts, expert_gate)
+
+    block.experts.forward = spy16
+    y16 = block(case.h.to(torch.bfloat16))
+    assert y16.dtype == torch.bfloat16
+    np.savez_compressed(
+        os.path.join(HERE, "moe_bf16act.npz"),
+        y=y16.float().numpy(),
+        experts=captured["experts"].numpy(),
+        gate=captured["gate"].float().numpy(),
+        digest=np.array(digest(case)),
+    )
+    print("moe_bf16act.npz written")
 
 
 if __name__ == "__main__":

@@ -152,3 +152,18 @@ def test_sampled_streamed_evaluation_equals_the_full_one(name):
     got, mid2 = orc.moe_block_sampled(case.h, p, lambda e: (p.w_gate[e], p.w_up[e], p.w_down[e]), sel)
     assert torch.equal(mid2["experts"], mid["experts"])
     assert orc.rel_l2(got, want.view(-1, case.spec.hidden)[sel]) < 1e-6
+
+
+def test_oracle_follows_the_reference_on_bf16_activations():
+    """With bf16 `h` the reference rounds the normalised row, the router logits
+    and the expert weights to bf16 (layers/norm.py:39-41, ops/default_impls.py:
+    332-333, :351).  The oracle makes the same casts: indices and outputs equal
+    the fixture sharktank produced."""
+    g = load_golden("moe_bf16act.npz")
+    spec = syn.CaseSpec("bf16act", 512, 256, 512, kind=syn.Q8_0, norm_weight="perturbed", seed=21)
+    case = syn.make_case(spec)
+    assert case_digest(case) == str(g["digest"])
+    y, mid = orc.moe_block(case.h.to(torch.bfloat16), oracle_params(case), form="pregather")
+    assert np.array_equal(mid["experts"].numpy(), g["experts"])
+    assert y.dtype == torch.bfloat16
+    assert orc.rel_l2(y.float(), torch.from_numpy(g["y"])) < 1e-6
