@@ -545,6 +545,108 @@ def main():
         e2e = {"value": tokens * layers * args.steps / dt, "unit": "tokens/s",
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "steps_in_flight": 1}
         l2_cold = None
+    elif args.workload == "stack32_decode64":
+        # ------------------- 32-layer stack, expert parallel (peer-to-peer)
+        from shark_platform_b200 import parallel
+        from shark_platform_b200.moe import B200MoeStack
+
+        layers = 32
+        per = tokens // world
+        case0 = syn.make_case_on_device(dataclasses.replace(spec, tokens=tokens, seed=999), dev)
+        h_all = syn.case_input(case0, dev).reshape(tokens, spec.hidden)
+        h = h_all[rank * per:(rank + 1) * per].contiguous()
+        # layer by layer: draw the full layer (same seed on every rank), route this
+        # rank's slice of the running activations through the single-GPU layer as
+        # the correctness witness, keep the expert shard, drop the rest
+        x = parallel.P2PExchange(spec.hidden, spec.experts, spec.top_k, tokens, per, dist.group.WORLD, dev)
+        blocks, rows = [], torch.zeros(spec.experts, device=dev)
+        want = h
+        for i in range(layers):
+            sp = dataclasses.replace(spec, tokens=tokens, router_bias="zipf", seed=1000 + i)
+            c = syn.make_case_on_device(sp, dev)
+            full = syn.case_block(c, args.regime, dev)
+            want, ex_i, _ = full.layer.forward(want, want_routing=True)
+            rows += torch.bincount(ex_i.reshape(-1).to(torch.int64), minlength=spec.experts).float()
+            del full
+            blocks.append(parallel.build_from_case(c, dist.group.WORLD, args.regime, "p2p", per, x))
+            del c
+            torch.cuda.empty_cache()
+        stack = parallel.ExpertParallelStack(blocks)
+        step = lambda: stack(h)
+        launches_per_step = blocks[0].launches_per_step * layers
+        y = step()
+        num = torch.linalg.norm((y.float() - want.float()).double()) ** 2
+        den = torch.linalg.norm(want.float().double()) ** 2
+        agg = torch.stack([num, den])
+        dist.all_reduce(agg)
+        ep_check = {"rel_l2_vs_single_gpu": float(torch.sqrt(agg[0] / agg[1])),
+                    "what": "every rank's token slice through the 32 full single-GPU layers vs the "
+                            "expert-parallel stack, all ranks' tokens together"}
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        moe.device_status()
+        if rank == 0:
+            sampler.start()
+        for _ in range(40):  # ~0.5 s of the same load on every rank before timing
+            step()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            y = step()
+        ev1.record()
+        barrier()
+        t = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item()) / args.steps
+        value = tokens * layers / (ms_step * 1e-3)
+        moe.device_status()
+        stage = stage_times(C, step, min(args.steps, 512 // layers))
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+        if clocks is not None:
+            clocks["window"] = "40 steps of the same load before the timed region, the timed region, the stage-event pass"
+        dist.all_reduce(rows)
+        per_rank = rows.view(world, -1).sum(dim=1)
+        # every rank streams the weights of its own experts once per layer call
+        el = spec.experts // world
+        rank_bytes = el * 3 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
+        gu = torch.tensor([stage["gate_up"]], device=dev)
+        dist.all_reduce(gu, op=dist.ReduceOp.MAX)
+        ach = el * 2 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden) / (float(gu.item()) * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "gate_up", "achieved": ach, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                    "note": "per GPU: this rank's expert weights over the slowest rank's gate/up time",
+                    "peak_source": peaks["source"] + " (copy)"}
+        whole = {"hbm_frac_per_gpu": layers * rank_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                 "ep_check": ep_check,
+                 "rows_per_rank": {"max": float(per_rank.max()), "mean": float(per_rank.mean()),
+                                   "note": "rows routed to each rank's experts, summed over the 32 layers"}}
+        stage = {"rank0": stage}
+        hp = h.cpu().pin_memory()
+        yp = torch.empty_like(hp).pin_memory()
+        h_dev = torch.empty_like(h)
+        nbytes = hp.numel() * hp.element_size()
+
+        def e2e_step():
+            h_dev.copy_(hp, non_blocking=True)
+            yp.copy_(stack(h_dev), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        barrier()
+        dt = torch.tensor([time.perf_counter() - t0], device=dev)
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {"value": tokens * layers * args.steps / float(dt.item()), "unit": "tokens/s",
+               "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": nbytes * world,
+               "steps_in_flight": 1}
+        l2_cold = None
     else:
         # ------------------------------------------------ expert parallelism
         from shark_platform_b200 import parallel

@@ -29,7 +29,13 @@
 //               tensor-memory store latency hides behind the other's arithmetic
 //   warp  16    TMA producer for weights and scales
 //   warp  17    TMA producer for token tiles
-//   warp  18    TMEM allocation; one lane issues the MMAs and commits
+//   warp  18    TMEM allocation; one lane issues the MMAs of row set 0 and commits
+//   warp  19    one lane issues the MMAs of row set 1
+// Two issuers because issuing is what the loop is short of: an MMA costs its
+// issuing thread ~70 clocks, eight per 64-k stage plus the barrier waits exceed
+// the 768 clocks the tensor pipe needs for them, so with one issuer the pipe runs
+// dry every stage.  Each row set has its own A-slot barriers, so the two sets
+// are independent pipelines that share only the token tiles.
 //
 // Tensor-memory columns (512 allocated): accumulators at 0 and 192 (192 fp32
 // columns each), two A staging slots of 2 x 32 columns at 384..511.
@@ -44,8 +50,9 @@ namespace {
 constexpr int TC_DQ_WARPS = 16;
 constexpr int TC_WARP_WPROD = TC_DQ_WARPS;
 constexpr int TC_WARP_XPROD = TC_DQ_WARPS + 1;
-constexpr int TC_WARP_MMA = TC_DQ_WARPS + 2;
-constexpr int TC_THREADS = (TC_DQ_WARPS + 3) * 32;
+constexpr int TC_WARP_MMA = TC_DQ_WARPS + 2;   // issues the MMAs of row set 0 (and owns the TMEM allocation)
+constexpr int TC_WARP_MMA1 = TC_DQ_WARPS + 3;  // issues the MMAs of row set 1
+constexpr int TC_THREADS = (TC_DQ_WARPS + 4) * 32;
 constexpr int TC_KT = 64;            // k per stage (one token slot, one A slot)
 constexpr int TC_ROWS = 128;         // weight rows per set
 constexpr int TC_NTOK = 192;         // largest token tile / accumulator width
@@ -77,7 +84,7 @@ struct TcCfg {
   static constexpr uint32_t COL_ACC0 = 0, COL_ACC1 = NMAX, COL_A = 2 * NMAX;
   static_assert(XSLOT % 1024 == 0 && TC_WSLOT % 1024 == 0, "slot alignment for the swizzle");
   static_assert(SMEM <= 232448, "shared memory budget");
-  static_assert(2 * (WSLOTS + XSLOTS + TC_SSLOTS + ASLOTS) + 2 <= 64, "barrier area");
+  static_assert(2 * (WSLOTS + XSLOTS + TC_SSLOTS + 2 * ASLOTS) + 2 <= 64, "barrier area");
 };
 
 struct TcArgs {
@@ -210,7 +217,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   const uint32_t wfull = take(TC_WSLOTS), wempty = take(TC_WSLOTS);
   const uint32_t xfull = take(TC_XSLOTS), xempty = take(TC_XSLOTS);
   const uint32_t sfull = take(TC_SSLOTS), sempty = take(TC_SSLOTS);
-  const uint32_t a_ready = take(TC_ASLOTS), a_free = take(TC_ASLOTS);
+  const uint32_t a_ready = take(2 * TC_ASLOTS), a_free = take(2 * TC_ASLOTS);  // [slot][row set]
   const uint32_t acc_full_bar = take(1), acc_empty_bar = take(1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -222,17 +229,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     }
     for (int s = 0; s < TC_XSLOTS; ++s) {
       mbar_init(xfull + 8u * s, 1);
-      mbar_init(xempty + 8u * s, 1);
+      mbar_init(xempty + 8u * s, 2);  // both issuers commit
     }
     for (int s = 0; s < TC_SSLOTS; ++s) {
       mbar_init(sfull + 8u * s, 1);
       mbar_init(sempty + 8u * s, TC_DQ_WARPS);
     }
-    for (int s = 0; s < TC_ASLOTS; ++s) {
-      mbar_init(a_ready + 8u * s, TC_DQ_WARPS / 2);  // one arrival per warp of the group that fills the slot
+    for (int s = 0; s < 2 * TC_ASLOTS; ++s) {
+      mbar_init(a_ready + 8u * s, TC_DQ_WARPS / 4);  // one arrival per warp of the group and row set that fills it
       mbar_init(a_free + 8u * s, 1);
     }
-    mbar_init(acc_full_bar, 1);
+    mbar_init(acc_full_bar, 2);  // both issuers commit
     mbar_init(acc_empty_bar, TC_DQ_WARPS);  // one arrival per dequant warp
     fence_mbar_init();
     int run = 0;
@@ -355,9 +362,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
       for (uint32_t i = n > (uint32_t)TC_XSLOTS ? n - TC_XSLOTS : 0; i < n; ++i)
         mbar_wait(xfull + 8u * (i % TC_XSLOTS), (i / TC_XSLOTS) & 1u, abort_flag, args.status);
     }
-  } else if (warp == TC_WARP_MMA) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == TC_WARP_MMA || warp == TC_WARP_MMA1) {
+    // ------------------------------------------ MMA issuers, one per row set
     if (lane == 0) {
+      const int mset = warp - TC_WARP_MMA;
+      const uint32_t acc = tmem + (mset == 0 ? TC_COL_ACC0 : TC_COL_ACC1);
       uint32_t n = 0, ti = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
@@ -369,8 +378,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
         for (int st = 0; st < stages_per_tile; ++st, ++n) {
           const int xs = n % TC_XSLOTS;
           const int as = n % TC_ASLOTS;
+          const uint32_t ab = 8u * (2 * as + mset);
           if (!mbar_wait(xfull + 8u * xs, (n / TC_XSLOTS) & 1u, abort_flag, args.status) ||
-              !mbar_wait(a_ready + 8u * as, (n / TC_ASLOTS) & 1u, abort_flag, args.status)) {
+              !mbar_wait(a_ready + ab, (n / TC_ASLOTS) & 1u, abort_flag, args.status)) {
             ok = false;
             break;
           }
@@ -380,12 +390,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           for (int j = 0; j < TC_KT / 16; ++j) {
             const uint32_t accum = (st > 0 || j > 0) ? 1u : 0u;
             const uint64_t bd = bdesc + static_cast<uint64_t>((j * 32) >> 4);
-            const uint32_t a0 = tmem + TC_COL_A + as * 64 + j * 8;
-            tc_mma_ts(tmem + TC_COL_ACC0, a0, bd, idesc, accum);
-            tc_mma_ts(tmem + TC_COL_ACC1, a0 + 32, bd, idesc, accum);
+            tc_mma_ts(acc, tmem + TC_COL_A + as * 64 + mset * 32 + j * 8, bd, idesc, accum);
           }
           tc_commit(xempty + 8u * xs);
-          tc_commit(a_free + 8u * as);
+          tc_commit(a_free + ab);
         }
         if (ok) tc_commit(acc_full_bar);
       }
@@ -462,7 +470,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
               for (int j = 0; j < 4; ++j)
                 dequant_q8x4(q[c][j], c < 2 ? s_lo : s_hi, v[c * 8 + 2 * j], v[c * 8 + 2 * j + 1]);
           }
-          if (!mbar_wait_warp(a_free + 8u * as, ((n / TC_ASLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
+          if (!mbar_wait_warp(a_free + 8u * (2 * as + set), ((n / TC_ASLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
           tc_fence_after();
           tmem_st32(tmem + lane_addr + TC_COL_A + as * 64 + set * 32, v);
           tmem_wait_st();
@@ -470,7 +478,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           // one arrival per warp: 256 arrivals per stage on one barrier word
           // serialise in shared memory
           __syncwarp();
-          if (lane == 0) mbar_arrive(a_ready + 8u * as);
+          if (lane == 0) mbar_arrive(a_ready + 8u * (2 * as + set));
         }
       }
       if (!ok) break;

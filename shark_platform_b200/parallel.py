@@ -320,6 +320,25 @@ class P2PExpertParallelMoeBlock(torch.nn.Module):
         return y.reshape(shape)
 
 
+class ExpertParallelStack(torch.nn.Module):
+    """Several expert-parallel MoE layers applied back to back on this rank's
+    tokens (the MoE halves of consecutive transformer blocks): the output of
+    layer i is the input of layer i+1.  Peer-to-peer layers share one
+    `P2PExchange` — one set of symmetric buffers and one epoch counter for the
+    whole stack."""
+
+    def __init__(self, blocks):
+        super().__init__()
+        self.blocks = torch.nn.ModuleList(blocks)
+        xs = {id(b.x) for b in blocks if isinstance(b, P2PExpertParallelMoeBlock)}
+        assert len(xs) <= 1, "peer-to-peer layers of a stack must share their exchange"
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        for blk in self.blocks:
+            h = blk(h)
+        return h
+
+
 def shard_theta(theta, rank: int):
     """This rank's view of a (possibly sharded) theta: `SplitPrimitiveTensor` /
     `ReplicatedTensor` entries are replaced by their shard for `rank`."""
@@ -390,3 +409,15 @@ def build_from_case(case, group=None, regime: str = "auto", transport: str = "nc
     tokens = case.h.shape[1]
     return build_block(T.Theta(tree), s.experts, s.top_k, s.eps, s.activation, group, regime,
                        transport, tokens, max_local_tokens or -(-tokens // world), exchange)
+
+
+def build_stack_from_cases(cases, group=None, regime: str = "auto", max_local_tokens: int = 0):
+    """Benchmark/test helper: a stack of peer-to-peer expert-parallel layers, one
+    per synthetic case (same shape), sharing one exchange."""
+    group = group if group is not None else dist.group.WORLD
+    world = dist.get_world_size(group)
+    s = cases[0].spec
+    tokens = cases[0].h.shape[1]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    x = P2PExchange(s.hidden, s.experts, s.top_k, tokens, max_local_tokens or -(-tokens // world), group, dev)
+    return ExpertParallelStack([build_from_case(c, group, regime, "p2p", max_local_tokens, x) for c in cases])

@@ -124,3 +124,62 @@ def test_barrier_gives_up_when_a_peer_never_arrives():
     y = blk(syn.case_input(case))
     assert torch.isfinite(y.float()).all()
     assert moe.device_status() == 0
+
+
+@pytest.mark.parametrize("name,tokens", [("small_q8", 40), ("small_grok", 130), ("small_q4k", 300)])
+def test_single_call_expert_parallel_layer_with_one_rank(name, tokens):
+    """`b200moe_ep_layer_forward` with a world of one: the whole sequence
+    (publish, three barriers, dispatch, grouped products, return, combine) runs on
+    one GPU with nobody to wait for, and must reproduce the ordinary layer up to
+    the bf16 rounding of the returned rows.  Called three times in a row with
+    advancing epochs, the way a stack of layers shares one exchange."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from oracle import moe_oracle as orc
+    from helpers import oracle_params
+    from shark_platform_b200 import _cabi as C, moe, synthetic as syn
+
+    case = syn.make_case(syn.CASES[name], tokens=tokens)
+    s = case.spec
+    blk = syn.case_block(case)
+    layer = blk.layer
+    h = syn.case_input(case).reshape(tokens, s.hidden).contiguous()
+    want = blk.layer.forward(h)
+    ref, _ = orc.moe_block(case.h, oracle_params(case), form="per_expert")
+    E, k, d = s.experts, s.top_k, s.hidden
+    cap, ret_rows = tokens * k, tokens * k
+    counts_all = torch.zeros(1, E, dtype=torch.int32, device="cuda")
+    flags = torch.zeros(1, dtype=torch.int32, device="cuda")
+    recv = torch.zeros(cap, d, dtype=torch.float16, device="cuda")
+    ret = torch.zeros(ret_rows, d, dtype=torch.bfloat16, device="cuda")
+    ep = C.EpDesc()
+    ep.world, ep.rank, ep.experts_local = 1, 0, E
+    ep.counts_all[0], ep.flags[0] = counts_all.data_ptr(), flags.data_ptr()
+    ep.recv_x[0], ep.ret_y[0] = recv.data_ptr(), ret.data_ptr()
+    desc = ctypes.byref(layer.desc)
+    ks = C.lib.b200moe_down_ksplit(ctypes.byref(layer.down.desc), tokens * k, tokens, C.REGIME_AUTO)
+    nbytes = C.lib.b200moe_ep_workspace_bytes(desc, tokens, cap, ks)
+    assert nbytes > 0
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    dt = C.DT_BF16 if h.dtype == torch.bfloat16 else C.DT_F32
+    epoch = 0
+    for _ in range(3):
+        y = torch.zeros_like(h)
+        C.check(C.lib.b200moe_ep_layer_forward(desc, ctypes.byref(ep), p(h), p(y), dt, tokens, C.REGIME_AUTO,
+                                               cap, ret_rows, tokens, ks, epoch, p(ws), nbytes, st),
+                "ep_layer_forward")
+        epoch += 3
+        torch.cuda.synchronize()
+        assert moe.device_status() == 0
+        assert orc.rel_l2(y.float().cpu(), want.float().cpu()) < 1e-2
+        assert orc.rel_l2(y.float().cpu().view(1, tokens, d), ref) < 2e-2
+    assert int(flags[0]) == epoch
+    # too small a workspace or return buffer is refused before anything is launched
+    rc = C.lib.b200moe_ep_layer_forward(desc, ctypes.byref(ep), p(h), p(y), dt, tokens, C.REGIME_AUTO,
+                                        cap, ret_rows, tokens, ks, epoch, p(ws), nbytes - 1, st)
+    assert rc == -3
+    rc = C.lib.b200moe_ep_layer_forward(desc, ctypes.byref(ep), p(h), p(y), dt, tokens, C.REGIME_AUTO,
+                                        cap, ret_rows - 1, tokens, ks, epoch, p(ws), nbytes, st)
+    assert rc == -1 and "return buffer" in C.last_error()
