@@ -294,11 +294,14 @@ def roofline_single(syn, spec, tokens, stage, peaks, experts_total=None):
     if tokens >= 512:
         gu_flops = tokens * spec.top_k * 2 * 2 * spec.ffn * spec.hidden
         ach = gu_flops / (stage["gate_up"] * 1e-3) / 1e12
-        peak = peaks["bf16_tflops"]
+        # the kernel is timed inside a long run at the settled clock (SOAK_S of the
+        # same steps come first), so the denominator is the sustained cuBLAS figure
+        peak = peaks["bf16_tflops_sustained"]
         return {"bound": "tensor", "kernel": "gate_up", "achieved": ach, "peak": peak,
                 "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-                "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
-                "peak_source": peaks["source"] + " (cuBLAS bf16 burst)"}
+                "frac_of_burst": ach / peaks["bf16_tflops"],
+                "peak_source": peaks["source"] + " (cuBLAS bf16, sustained under the power cap; "
+                               f"burst {peaks['bf16_tflops']})"}
     gu_bytes = experts_active * 2 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
     ach = gu_bytes / (stage["gate_up"] * 1e-3) / 1e9
     peak = peaks["hbm_gbs"]
@@ -363,7 +366,8 @@ def measure_layer(C, moe, syn, block, h, spec, args, peaks, sampler=None, cold=T
     experts_active = min(spec.experts, tokens * spec.top_k)
     layer_bytes = (experts_active * 3 * syn.weight_bytes(spec.kind, spec.ffn, spec.hidden)
                    + 2 * tokens * spec.hidden * 2 + spec.experts * spec.hidden * 4)
-    out["whole_layer"] = {"tensor_frac": flops / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
+    out["whole_layer"] = {"tensor_frac": flops / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                          "tensor_frac_of_burst": flops / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
                           "hbm_frac": layer_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     regime = moe.REGIMES[args.regime]
     e2e, y_host = e2e_pipeline(C, moe, block.layer, h, args.steps, regime, depth=2)
@@ -560,12 +564,14 @@ def main():
         # the correctness witness, keep the expert shard, drop the rest
         x = parallel.P2PExchange(spec.hidden, spec.experts, spec.top_k, tokens, per, dist.group.WORLD, dev)
         blocks, rows = [], torch.zeros(spec.experts, device=dev)
-        want = h
+        want, inputs, wants = h, [], []
         for i in range(layers):
             sp = dataclasses.replace(spec, tokens=tokens, router_bias="zipf", seed=1000 + i)
             c = syn.make_case_on_device(sp, dev)
             full = syn.case_block(c, args.regime, dev)
+            inputs.append(want)
             want, ex_i, _ = full.layer.forward(want, want_routing=True)
+            wants.append(want)
             rows += torch.bincount(ex_i.reshape(-1).to(torch.int64), minlength=spec.experts).float()
             del full
             blocks.append(parallel.build_from_case(c, dist.group.WORLD, args.regime, "p2p", per, x))
@@ -574,14 +580,20 @@ def main():
         stack = parallel.ExpertParallelStack(blocks)
         step = lambda: stack(h)
         launches_per_step = blocks[0].launches_per_step * layers
-        y = step()
-        num = torch.linalg.norm((y.float() - want.float()).double()) ** 2
-        den = torch.linalg.norm(want.float().double()) ** 2
-        agg = torch.stack([num, den])
-        dist.all_reduce(agg)
-        ep_check = {"rel_l2_vs_single_gpu": float(torch.sqrt(agg[0] / agg[1])),
-                    "what": "every rank's token slice through the 32 full single-GPU layers vs the "
-                            "expert-parallel stack, all ranks' tokens together"}
+        # witness per layer, every layer fed the single-GPU chain's own input (a
+        # chain of 32 random layers amplifies a rounding difference into different
+        # expert choices further down, so end-to-end distance is not a measure)
+        worst = torch.zeros(1, device=dev)
+        for blk, xin, ref_out in zip(blocks, inputs, wants):
+            got = blk(xin)
+            agg = torch.stack([torch.linalg.norm((got.float() - ref_out.float()).double()) ** 2,
+                               torch.linalg.norm(ref_out.float().double()) ** 2])
+            dist.all_reduce(agg)
+            worst = torch.maximum(worst, torch.sqrt(agg[0] / agg[1]).float().reshape(1))
+        ep_check = {"rel_l2_vs_single_gpu": float(worst.item()),
+                    "what": "largest over the 32 layers: each expert-parallel layer against the full "
+                            "single-GPU layer on the same input (the single-GPU chain's), all ranks' tokens"}
+        del inputs, wants
         for _ in range(args.warmup):
             step()
         barrier()
@@ -734,10 +746,11 @@ def main():
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         gu_flops = float(tokens * spec.top_k) * 2 * 2 * spec.ffn * spec.hidden
         ach = gu_flops / (float(tt[0].item()) * 1e-3) / 1e12
-        peak = peaks["bf16_tflops"] * world
+        peak = peaks["bf16_tflops_sustained"] * world
         roofline = {"bound": "tensor", "kernel": "gate_up", "achieved": ach, "peak": peak,
                     "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-                    "peak_source": peaks["source"] + f" (cuBLAS bf16 burst x {world} GPUs)"}
+                    "frac_of_burst": ach / (peaks["bf16_tflops"] * world),
+                    "peak_source": peaks["source"] + f" (cuBLAS bf16, sustained under the power cap, x {world} GPUs)"}
         stage = {"gate_up_max_over_ranks": float(tt[0].item()), "down_max_over_ranks": float(tt[1].item()),
                  "rank0": st_ms}
         flops = syn.layer_flops(tokens, spec.top_k, spec.hidden, spec.ffn)

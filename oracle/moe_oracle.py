@@ -28,6 +28,7 @@ import torch.nn.functional as F
 
 Q8_0 = "Q8_0"
 Q4_K = "Q4_K"
+Q4_1 = "Q4_1"
 DENSE = "DENSE"
 
 # --------------------------------------------------------------------------
@@ -188,6 +189,20 @@ def q8_0_dequant(planes: dict, dtype=np.float16) -> np.ndarray:
     prod = d.astype(np.float32) * qs.astype(np.float32)  # exact: 11 x 8 bits
     out = prod.astype(dtype)
     return out.reshape(out.shape[:-2] + (out.shape[-2] * out.shape[-1],))
+
+
+def q4_1_dequant(planes: dict) -> np.ndarray:
+    """BlockScaledI4Layout (types/layouts.py:303-347, unsigned, with offsets `m`:
+    GGUF Q4_1): `qs` holds two 4-bit values per byte, low nibble first
+    (layout_utils.py:67-86), and dequant is BlockScaledLayout's
+    `d * qs + m` evaluated in fp16 (types/layouts.py:277-290): one rounding after
+    the product, one after the sum."""
+    d = np.asarray(planes["d"]).astype(np.float32)
+    m = np.asarray(planes["m"]).astype(np.float32)
+    q = unpack_i4(planes["qs"]).astype(np.float32)  # [..., K/32, 32]
+    h = lambda a: a.astype(np.float16).astype(np.float32)
+    w = h(h(d * q) + m).astype(np.float16)
+    return w.reshape(w.shape[:-2] + (w.shape[-2] * w.shape[-1],))
 
 
 def q4_k_fields(planes: dict) -> tuple[np.ndarray, np.ndarray, np.ndarray]:

@@ -134,6 +134,24 @@ def prepare_weight(t: Any, tile_scales: bool = True) -> PreparedWeight:
                                                   _stream()), "q4k_prepare")
             desc = C.WeightDesc(C.LAYOUT_Q4_K, e, n, k, qs.data_ptr(), None, sub.data_ptr())
             prep = PreparedWeight(desc, C.LAYOUT_Q4_K, e, n, k, (qs, sub))
+        elif name == "BlockScaledI4Layout":
+            # GGUF Q4_1: w = fp16(fp16(d*q) + m) per block of 32, two quants per byte,
+            # low nibble first — the nibble order of the Q4_K planar plane and the
+            # same two roundings as its fp16(fp16(ds*q) - dm), so it runs on the Q4_K
+            # kernels with the per-block pairs (d, -m)
+            lay = t.unpack()
+            if getattr(lay, "signed", False):
+                raise C.B200MoeError("signed BlockScaledI4Layout is not supported")
+            if k % 256 != 0:
+                raise C.B200MoeError(f"BlockScaledI4Layout: cols ({k}) must be a multiple of 256")
+            qs = planes["qs"].contiguous().view(torch.uint8)
+            d = planes["d"].contiguous().to(torch.float16).reshape(-1)
+            assert qs.numel() == e * n * k // 2 and d.numel() == e * n * k // 32
+            m = planes.get("m")
+            neg_m = torch.zeros_like(d) if m is None else -m.contiguous().to(torch.float16).reshape(-1)
+            sub = torch.stack([d, neg_m], dim=1).contiguous()
+            desc = C.WeightDesc(C.LAYOUT_Q4_K, e, n, k, qs.data_ptr(), None, sub.data_ptr())
+            prep = PreparedWeight(desc, C.LAYOUT_Q4_K, e, n, k, (qs, sub))
         else:
             raise C.B200MoeError(f"unsupported quantized layout {name}")
     try:
@@ -162,6 +180,8 @@ def dequant_layout(layout, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         for v in shape[:-2]:
             lead *= int(v)
         h.shape = [lead] + shape[-2:]
+    if type(layout).__name__ == "BlockScaledI4Layout" and dtype not in (None, torch.float16):
+        raise C.B200MoeError("BlockScaledI4Layout dequantises to fp16 only")
     prep = prepare_weight(h)
     is_q4k = prep.layout == C.LAYOUT_Q4_K
     out_dtype = torch.float16 if (dtype is None or is_q4k) else dtype
@@ -454,7 +474,7 @@ class ShardedGatheredExperts:
         self.shape = [t, k, int(base.shape[1]), int(base.shape[2])]
 
 
-_SUPPORTED = ("BlockScaledLayout", "SuperBlockOffsetScaled_4_6_Layout")
+_SUPPORTED = ("BlockScaledLayout", "SuperBlockOffsetScaled_4_6_Layout", "BlockScaledI4Layout")
 
 
 def get_index_quantized(tensor, key):

@@ -391,6 +391,8 @@ def build_from_case(case, group=None, regime: str = "auto", transport: str = "nc
         p = {name: v[e0:e1].contiguous().to(dev) for name, v in planes.items()}
         if s.kind == Q8_0:
             lay = T.BlockScaledLayout(shape, p["d"], p["qs"])
+        elif s.kind == "Q4_1":
+            lay = T.BlockScaledI4Layout(shape, p["d"], p["qs"], m=p["m"])
         else:
             lay = T.SuperBlockOffsetScaled_4_6_Layout(shape, **p)
         return T.PlanarQuantizedTensor(shape=shape, layout=lay)

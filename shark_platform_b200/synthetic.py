@@ -17,6 +17,7 @@ import torch
 
 Q8_0 = "Q8_0"
 Q4_K = "Q4_K"
+Q4_1 = "Q4_1"
 DENSE = "DENSE"
 
 
@@ -59,6 +60,9 @@ CASES = {
     "small_top4": CaseSpec(
         "small_top4", 29, 256, 512, kind=Q8_0, top_k=4, router_bias="normal",
         norm_weight="perturbed", seed=14,
+    ),
+    "small_q41": CaseSpec(
+        "small_q41", 37, 256, 512, kind=Q4_1, norm_weight="perturbed", seed=16
     ),
     "small_dense": CaseSpec(
         "small_dense", 21, 256, 512, kind=DENSE, act_dtype="f32",
@@ -107,11 +111,22 @@ def q4_k_planes(gen, experts: int, n: int, k: int) -> dict:
     }
 
 
+def q4_1_planes(gen, experts: int, n: int, k: int) -> dict:
+    """GGUF Q4_1 as sharktank holds it (BlockScaledI4Layout, types/layouts.py:
+    303-347): blocks of 32 unsigned 4-bit quants packed two per byte, fp16 scale
+    d = |N(0,1)|*0.02 and fp16 offset m = -7.5*d*(1 + 0.1*N(0,1)) (roughly zero-mean
+    weights of the size of the other layouts')."""
+    qs = torch.randint(0, 256, (experts, n, k // 32, 16), generator=gen, dtype=torch.uint8)
+    d32 = torch.randn(experts, n, k // 32, 1, generator=gen).abs() * 0.02
+    m32 = -7.5 * d32 * (1.0 + 0.1 * torch.randn(experts, n, k // 32, 1, generator=gen))
+    return {"d": d32.to(torch.float16), "m": m32.to(torch.float16), "qs": qs}
+
+
 def dense_planes(gen, experts: int, n: int, k: int) -> dict:
     return {"w": torch.randn(experts, n, k, generator=gen) * 0.02}
 
 
-_PLANE_MAKERS = {Q8_0: q8_0_planes, Q4_K: q4_k_planes, DENSE: dense_planes}
+_PLANE_MAKERS = {Q8_0: q8_0_planes, Q4_K: q4_k_planes, Q4_1: q4_1_planes, DENSE: dense_planes}
 
 
 @dataclass
@@ -163,6 +178,8 @@ def weight_bytes(kind: str, n: int, k: int) -> int:
         return n * k // 32 * 34
     if kind == Q4_K:
         return n * k // 256 * 144
+    if kind == Q4_1:
+        return n * k // 32 * 20
     return n * k * 2  # dense weights are held as fp16 on the device
 
 
@@ -186,6 +203,8 @@ def case_theta(case: Case, device="cuda"):
         p = {k: v.to(device) for k, v in planes.items()}
         if s.kind == Q8_0:
             lay = T.BlockScaledLayout(shape, p["d"], p["qs"])
+        elif s.kind == Q4_1:
+            lay = T.BlockScaledI4Layout(shape, p["d"], p["qs"], m=p["m"])
         else:
             lay = T.SuperBlockOffsetScaled_4_6_Layout(shape, **p)
         return T.PlanarQuantizedTensor(shape=shape, layout=lay)

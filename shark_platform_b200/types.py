@@ -124,6 +124,44 @@ class SuperBlockOffsetScaled_4_6_Layout(QuantizedLayout):
         return self._planes["qs"]
 
 
+class BlockScaledI4Layout(QuantizedLayout):
+    """types/layouts.py:303-347: a BlockScaledLayout whose `qs` are packed two
+    4-bit values per byte (low nibble first), blocks of 32 with fp16 scale `d`
+    and optional fp16 offset `m` (GGUF Q4_1).  Planes: `d`, `m` [..., K/32, 1],
+    `qs` [..., K/32, 16] uint8.  Only the unsigned form is supported by the CUDA
+    path."""
+
+    def __init__(self, shape, d, qs, *, m=None, signed: bool = False):
+        self._shape, self._d, self._qs, self._m, self.signed = list(shape), d, qs, m, signed
+
+    @classmethod
+    def serialized_name(cls) -> str:
+        return "BlockScaledI4Layout"
+
+    @property
+    def planes(self):
+        p = {"d": self._d, "qs": self._qs}
+        if self._m is not None:
+            p["m"] = self._m
+        return p
+
+    @property
+    def shape(self):
+        return self._shape
+
+    @property
+    def d(self):
+        return self._d
+
+    @property
+    def m(self):
+        return self._m
+
+    @property
+    def qs_bit_packed(self):
+        return self._qs
+
+
 class InferenceTensor:
     """types/tensors.py:189-454 (name, shape, indexing through ops.get_index)."""
 

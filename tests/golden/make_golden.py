@@ -61,6 +61,7 @@ def main():
     from sharktank.types import DefaultPrimitiveTensor, PlanarQuantizedTensor, Theta
     from sharktank.types.gguf_interop.layouts import Q4_K as RefQ4K, Q8_0 as RefQ8
     from sharktank.types.layouts import (
+        BlockScaledI4Layout,
         BlockScaledLayout,
         SuperBlockOffsetScaled_4_6_Layout,
     )
@@ -94,6 +95,15 @@ def main():
     out["q4k_qs_i8"] = lay4.qs.numpy()
     out["q4k_dequant_f16"] = lay4.dequant().numpy()
 
+    # Q4_1 as sharktank holds it: BlockScaledI4Layout with offsets
+    gq = torch.Generator().manual_seed(77)
+    p41 = syn.q4_1_planes(gq, 1, n, k)
+    lay41 = BlockScaledI4Layout([n, k], p41["d"][0], p41["qs"][0], m=p41["m"][0])
+    out["q41_d"] = p41["d"][0].numpy()
+    out["q41_m"] = p41["m"][0].numpy()
+    out["q41_qs"] = p41["qs"][0].numpy()
+    out["q41_dequant_f16"] = lay41.dequant().numpy()
+
     b = rng.integers(0, 256, size=(5, 16), dtype=np.uint8)
     tb = torch.from_numpy(b)
     out["bits_in"] = b
@@ -112,12 +122,14 @@ def main():
             lay = BlockScaledLayout(shape, planes["d"], planes["qs"])
         elif kind == syn.Q4_K:
             lay = SuperBlockOffsetScaled_4_6_Layout(shape, **planes)
+        elif kind == syn.Q4_1:
+            lay = BlockScaledI4Layout(shape, planes["d"], planes["qs"], m=planes["m"])
         else:
             return DefaultPrimitiveTensor(data=planes["w"])
         qt = PlanarQuantizedTensor(shape=shape, layout=lay)
         return DefaultPrimitiveTensor(data=qt.unpack().dequant())
 
-    for name in ["toy", "small_q8", "small_q4k", "small_grok", "small_top4", "small_dense"]:
+    for name in ["toy", "small_q8", "small_q4k", "small_q41", "small_grok", "small_top4", "small_dense"]:
         spec = syn.CASES[name]
         case = syn.make_case(spec)
         e, f, d = spec.experts, spec.ffn, spec.hidden

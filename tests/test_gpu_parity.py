@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 
 REL_L2_TOL = 2e-2  # layer output vs the fp32 reference path (fp16 operands, fp32 accumulate)
 GATE_TOL = 2e-6    # renormalised gates (fp32 softmax evaluated with a different exp)
-SMALL = ["small_q8", "small_q4k", "small_grok", "small_top4", "small_dense", "toy"]
+SMALL = ["small_q8", "small_q4k", "small_q41", "small_grok", "small_top4", "small_dense", "toy"]
 
 
 @pytest.fixture(scope="module")
@@ -38,6 +38,8 @@ def _planes_to_layout(kind, planes, shape, dev="cuda"):
     p = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in planes.items()}
     if kind == syn.Q8_0:
         return T.BlockScaledLayout(shape, p["d"], p["qs"])
+    if kind == syn.Q4_1:
+        return T.BlockScaledI4Layout(shape, p["d"], p["qs"], m=p["m"])
     return T.SuperBlockOffsetScaled_4_6_Layout(shape, **p)
 
 
@@ -58,10 +60,20 @@ def test_dequant_q4_k_bit_exact(M):
     assert np.array_equal(w.view(np.uint16), g["q4k_dequant_f16"].view(np.uint16))
 
 
-@pytest.mark.parametrize("kind", [syn.Q8_0, syn.Q4_K])
+def test_dequant_q4_1_bit_exact(M):
+    from shark_platform_b200 import types as T
+
+    g = load_golden("formats.npz")
+    cuda = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    lay = T.BlockScaledI4Layout([6, 512], cuda(g["q41_d"]), cuda(g["q41_qs"]), m=cuda(g["q41_m"]))
+    w = lay.dequant().cpu().numpy()
+    assert np.array_equal(w.view(np.uint16), g["q41_dequant_f16"].view(np.uint16))
+
+
+@pytest.mark.parametrize("kind", [syn.Q8_0, syn.Q4_K, syn.Q4_1])
 def test_dequant_random_planes_match_oracle(M, kind):
     gen = torch.Generator().manual_seed(5)
-    mk = syn.q8_0_planes if kind == syn.Q8_0 else syn.q4_k_planes
+    mk = {syn.Q8_0: syn.q8_0_planes, syn.Q4_K: syn.q4_k_planes, syn.Q4_1: syn.q4_1_planes}[kind]
     planes = mk(gen, 3, 40, 768)
     lay = _planes_to_layout(kind, np_planes(planes), [3, 40, 768])
     got = lay.dequant().cpu().numpy()
@@ -374,7 +386,7 @@ def test_ops_decline_unsupported():
 
 
 # ------------------------------------------------ tensor-memory (tcgen05) regime
-@pytest.mark.parametrize("name", ["small_q8", "small_grok", "small_top4", "small_q4k"])
+@pytest.mark.parametrize("name", ["small_q8", "small_grok", "small_top4", "small_q4k", "small_q41"])
 def test_tensor_regime_matches_reference_fixture(M, name):
     g = load_golden(f"moe_{name}.npz")
     case = syn.make_case(syn.CASES[name])

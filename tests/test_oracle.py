@@ -9,7 +9,7 @@ from oracle import moe_oracle as orc
 from shark_platform_b200 import synthetic as syn
 from helpers import case_digest, load_golden, oracle_params
 
-MOE_CASES = ["toy", "small_q8", "small_q4k", "small_grok", "small_top4", "small_dense"]
+MOE_CASES = ["toy", "small_q8", "small_q4k", "small_q41", "small_grok", "small_top4", "small_dense"]
 
 
 # ---- known-answer vectors from the reference's own tests -------------------
@@ -167,3 +167,11 @@ def test_oracle_follows_the_reference_on_bf16_activations():
     assert np.array_equal(mid["experts"].numpy(), g["experts"])
     assert y.dtype == torch.bfloat16
     assert orc.rel_l2(y.float(), torch.from_numpy(g["y"])) < 1e-6
+
+
+def test_q4_1_dequant_matches_reference():
+    """BlockScaledI4Layout with offsets (GGUF Q4_1), the one quantized MoE layout
+    the reference itself can index (ops/default_impls.py:204-218)."""
+    g = load_golden("formats.npz")
+    got = orc.q4_1_dequant({"d": g["q41_d"], "m": g["q41_m"], "qs": g["q41_qs"]})
+    assert np.array_equal(got.view(np.uint16), g["q41_dequant_f16"].view(np.uint16))
