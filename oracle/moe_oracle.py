@@ -245,6 +245,8 @@ def dequant(kind: str, planes: dict) -> np.ndarray:
         return q8_0_dequant(planes)
     if kind == Q4_K:
         return q4_k_dequant(planes)
+    if kind == Q4_1:
+        return q4_1_dequant(planes)
     raise ValueError(kind)
 
 
