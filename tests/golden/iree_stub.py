@@ -2,8 +2,9 @@
 
 Test scaffolding only: it exists so that `make_golden.py` and the optional
 reference cross-checks can import sharktank from a source checkout on a
-machine without iree-turbine.  Nothing here computes anything; the IREE custom
-kernels become callables that raise.  The product never imports this file.
+machine without iree-turbine.  The IREE custom kernels become callables that
+raise, except the rotary-embedding kernel, which has an eager stand-in so that
+the reference's whole model can run for the model-level test.  The product never imports this file.
 """
 import logging
 import sys
@@ -61,10 +62,36 @@ class ParameterArchiveBuilder(_Anything):
     add_blob = save = add_tensor
 
 
+def _eager_apply_rotary_embedding(input, table):
+    """Eager stand-in for the one IREE custom kernel the model-level test cannot
+    do without (kernels/rotary.py with templates/rotary_embedding.mlir): for
+    input [bs, sl, heads, dim] and angles table [bs, sl, dim], element pairs
+    (2i, 2i+1) are rotated, each output element using the angle stored at its
+    own index: out[2i] = x[2i]*cos(t[2i]) - x[2i+1]*sin(t[2i]),
+    out[2i+1] = x[2i+1]*cos(t[2i+1]) + x[2i]*sin(t[2i+1]).  Not checked against
+    IREE's output (iree-turbine is not installable here): the test that uses it
+    runs the same stand-in on both sides of its comparison."""
+    import torch
+
+    t = table.unsqueeze(2)
+    cos, sin = torch.cos(t), torch.sin(t)
+    real, imag = input[..., 0::2], input[..., 1::2]
+    out = torch.empty_like(input)
+    out[..., 0::2] = real * cos[..., 0::2] - imag * sin[..., 0::2]
+    out[..., 1::2] = imag * cos[..., 1::2] + real * sin[..., 1::2]
+    return out
+
+
+_EAGER = {"apply_rotary_embedding": _eager_apply_rotary_embedding}
+
+
 class CustomOp:
     @staticmethod
     def register(*, library=None, **_):
         def deco(cls):
+            if cls.__name__ in _EAGER:
+                return _EAGER[cls.__name__]
+
             def unavailable(*a, **k):
                 raise RuntimeError(f"iree stub: custom kernel {cls.__name__} unavailable")
 
