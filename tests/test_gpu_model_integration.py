@@ -103,10 +103,10 @@ def test_mixtral_model_with_every_moe_block_swapped(kind):
     reference = _build("cpu", kind, quantized=False)
     want_p, want_d, seq_lens = _prefill_and_decode(reference, "cpu")
 
-    model = _build("cuda", kind, quantized=True)
+    model = _build("cuda:0", kind, quantized=True)
     assert plugin.patch_moe_blocks(model) == BLOCKS
     assert all(isinstance(b, moe.B200MoeBlock) for b in model.moe_blocks)
-    got_p, got_d, _ = _prefill_and_decode(model, "cuda")
+    got_p, got_d, _ = _prefill_and_decode(model, "cuda:0")
     assert moe.device_status() == 0
     # positions past a sequence's length are padding: compare the valid ones
     for b, n in enumerate(seq_lens.tolist()):
