@@ -298,3 +298,51 @@ def make_case_on_device(spec: CaseSpec, device="cuda", seed: Optional[int] = Non
     else:
         raise NotImplementedError("device-side generation covers the quantized layouts")
     return Case(spec, h, norm_w, router_w, router_b, out_norm_w, planes(f, d), planes(f, d), planes(d, f))
+
+
+# ------------------------------------------------------------ attention block
+@dataclass
+class AttnCase:
+    """Seeded inputs of one paged attention block call sequence (a batched
+    prefill, then one decode step), shapes as in the reference's
+    PagedLlamaAttentionBlock (layers/paged_llama_attention_block.py:26-85)."""
+
+    hidden: int
+    head_count: int
+    head_count_kv: int
+    head_dim: int
+    stride: int
+    blocks: int
+    block_index: int
+    softcap: Optional[float]
+    h: torch.Tensor            # [bs, sl, d] prefill activations
+    h_decode: torch.Tensor     # [bs, 1, d]
+    seq_lens: torch.Tensor     # [bs]
+    page_ids: torch.Tensor     # [bs, pages per sequence] (room for the decode step)
+    pages: int
+    norm_w: torch.Tensor
+    wq: torch.Tensor
+    wk: torch.Tensor
+    wv: torch.Tensor
+    wo: torch.Tensor
+    eps: float = 1e-5
+    rope_base: float = 10000.0
+
+
+def make_attn_case(seed: int = 0, bs: int = 2, sl: int = 32, hidden: int = 256, head_count: int = 4,
+                   head_count_kv: int = 2, head_dim: int = 64, stride: int = 16, blocks: int = 2,
+                   block_index: int = 1, softcap: Optional[float] = None, seq_lens=None) -> AttnCase:
+    assert hidden == head_count * head_dim and sl % stride == 0
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s, sc=1.0: torch.randn(*s, generator=g) * sc
+    h, h_decode = rn(bs, sl, hidden), rn(bs, 1, hidden)
+    if seq_lens is None:
+        seq_lens = torch.tensor([sl - (7 * b) % sl for b in range(bs)])
+    per_seq = sl // stride + 1
+    pages = bs * per_seq + 3
+    page_ids = torch.randperm(pages, generator=g)[: bs * per_seq].view(bs, per_seq)
+    kv = head_count_kv * head_dim
+    return AttnCase(hidden, head_count, head_count_kv, head_dim, stride, blocks, block_index, softcap,
+                    h, h_decode, seq_lens, page_ids, pages,
+                    1.0 + 0.1 * rn(hidden), rn(hidden, hidden, sc=0.06), rn(kv, hidden, sc=0.06),
+                    rn(kv, hidden, sc=0.06), rn(hidden, hidden, sc=0.06))

@@ -10,6 +10,8 @@ Writes:
                    `unpack()` produces and its `dequant()` values; outputs of
                    the bit-unpack helpers on random bytes
   moe_bf16act.npz  sharktank's MoeBlock on bf16 activations (its bf16 router path)
+  attn_*.npz       sharktank's PagedLlamaAttentionBlock: prefill and decode outputs and
+                   the KV page slab after each
   moe_<case>.npz   outputs of sharktank's MoeBlock for the small seeded cases
                    of shark_platform_b200.synthetic (quantized weights go
                    through `layout.dequant()` -> DefaultPrimitiveTensor, the
@@ -204,6 +206,49 @@ def main():
         digest=np.array(digest(case)),
     )
     print("moe_bf16act.npz written")
+
+    # ---------------- paged attention block ----------------
+    # sharktank's own PagedLlamaAttentionBlock + PagedKVCache + RotaryEmbeddingLayer:
+    # a batched prefill, then one decode step on the cache it filled.  The rotary
+    # kernel is the eager stand-in of iree_stub.py (the IREE kernel cannot run).
+    from sharktank.layers import PagedKVCache, PagedLlamaAttentionBlock, RotaryEmbeddingLayer
+
+    for name, softcap in (("attn_plain", None), ("attn_softcap", 30.0)):
+        c = syn.make_attn_case(seed=70 if softcap is None else 71, softcap=softcap)
+        bs, sl, _ = c.h.shape
+        cache = PagedKVCache(transformer_block_count=c.blocks, attn_head_count=c.head_count_kv,
+                             attn_head_dim=c.head_dim, block_seq_stride=c.stride, dtype=torch.float32)
+        theta = Theta({
+            "attn_norm": {"weight": DefaultPrimitiveTensor(data=c.norm_w)},
+            "attn_q": {"weight": DefaultPrimitiveTensor(data=c.wq)},
+            "attn_k": {"weight": DefaultPrimitiveTensor(data=c.wk)},
+            "attn_v": {"weight": DefaultPrimitiveTensor(data=c.wv)},
+            "attn_output": {"weight": DefaultPrimitiveTensor(data=c.wo)},
+        })
+        block = PagedLlamaAttentionBlock(theta, block_index=c.block_index, cache=cache,
+                                         head_count=c.head_count, head_dim=c.head_dim,
+                                         head_count_kv=c.head_count_kv, rms_epsilon=c.eps, softcap=softcap)
+        rope = RotaryEmbeddingLayer(rope_dimension_count=c.head_dim, max_seqlen=256, rope_freq_base=c.rope_base)
+        state = cache.allocate(c.pages)
+        state[0].zero_()
+        neg = torch.finfo(torch.float32).min
+        causal = torch.triu(torch.ones(sl, sl, dtype=torch.bool), diagonal=1)[None, None]
+        pad = (torch.arange(sl)[None, :] >= c.seq_lens[:, None])[:, None, None, :]
+        mask = torch.where(causal | pad, neg, 0.0)
+        y = block(c.h, embedding=rope, start_index=0, attention_mask=mask, cache_state=state,
+                  seq_block_ids=c.page_ids[:, : sl // c.stride])
+        slab_prefill = state[0].clone()
+        kv_len = c.page_ids.shape[1] * c.stride
+        dmask = torch.where(torch.arange(kv_len)[None, :] >= (c.seq_lens + 1)[:, None], neg, 0.0)[:, None, None, :]
+        xk_temp = torch.zeros(bs, 256, c.head_count_kv, c.head_dim)
+        xv_temp = torch.zeros(bs, 256, c.head_count_kv, c.head_dim)
+        yd = block(c.h_decode, embedding=rope, start_positions=c.seq_lens,
+                   embedding_batch_mask=rope.compute_batch_mask(c.seq_lens, batch_seq_len=1),
+                   attention_mask=dmask, cache_state=state, seq_block_ids=c.page_ids,
+                   xk_temp=xk_temp, xv_temp=xv_temp)
+        np.savez_compressed(os.path.join(HERE, f"{name}.npz"), y=y.numpy(), slab_prefill=slab_prefill.numpy(),
+                            y_decode=yd.numpy(), slab_decode=state[0].numpy())
+        print(f"{name}.npz written  |y|={float(y.abs().mean()):.4f} |yd|={float(yd.abs().mean()):.4f}")
 
 
 if __name__ == "__main__":

@@ -100,6 +100,17 @@ def test_mixtral_model_with_every_moe_block_swapped(kind):
     from oracle import moe_oracle as orc
     from shark_platform_b200 import moe, plugin
 
+    # the reference builds its rotary table from a CPU `arange` whatever the
+    # device of the positions (layers/rotary_embedding.py:222-228), which stops its
+    # own model on CUDA; the same formula with the range on the positions' device
+    from sharktank.layers.rotary_embedding import RotaryEmbeddingLayer
+
+    def table_on_the_positions_device(self, t):
+        dim = self.rope_dimension_count
+        freqs = 1.0 / (self.rope_freq_base ** ((torch.arange(0, dim, device=t.device) // 2).float() / dim * 2.0))
+        return torch.outer(t, freqs).float()
+
+    RotaryEmbeddingLayer._compute_rotary_embed_table = table_on_the_positions_device
     reference = _build("cpu", kind, quantized=False)
     want_p, want_d, seq_lens = _prefill_and_decode(reference, "cpu")
 
