@@ -318,6 +318,62 @@ int b200moe_layer_forward_host(const b200moe_layer_t* layer, const void* h_host,
                                int io_dtype, int32_t tokens, int regime, void* dev_io,
                                void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- The attention block that precedes every MoE layer --------------------
+ * PagedLlamaAttentionBlock (layers/paged_llama_attention_block.py:26-303) with
+ * its paged KV cache (layers/kv_cache.py:222-526).  The projections are plain
+ * dense products and stay with the caller (a library GEMM, or the quantized
+ * linear of this library); these entry points cover the rest. */
+
+/* Geometry of a PagedKVCache page slab (layers/kv_cache.py:246-277): row `page`
+ * of the slab is [blocks][2: K, V][stride][kv_heads][head_dim]. */
+typedef struct {
+  int32_t blocks;     /* transformer_block_count */
+  int32_t stride;     /* block_seq_stride: positions per page */
+  int32_t kv_heads;   /* attn_head_count of the cache (kv heads) */
+  int32_t head_dim;
+  int32_t page_count; /* rows of the slab */
+} b200moe_kv_cache_t;
+
+/* RMSNormLayer.forward (layers/norm.py:34-41): y = w * (x * rsqrt(mean(x^2) +
+ * eps)) in fp32, x / y [rows, d] of x_dtype / y_dtype (F32, F16 or BF16). */
+int b200moe_rms_norm(const void* x, int x_dtype, const float* weight, int64_t rows, int32_t d, float eps,
+                     void* y, int y_dtype, void* stream);
+
+/* Rotary embedding of q and k (layers/rotary_embedding.py:115-240 with
+ * kernels/templates/rotary_embedding.mlir: pairs (2i, 2i+1), angle position *
+ * freqs[i]) fused with the cache write of PagedKVCache.write / write_timestep
+ * (layers/kv_cache.py:428-526).  q [tokens, heads, hd] is rotated in place; k is
+ * rotated and, like v, stored at its position's slot of page
+ * page_ids[seq, position / stride] for transformer block `block_index`; k_out /
+ * v_out (both or neither) receive the same rows contiguously (prefill attends
+ * them directly).  positions [tokens]: absolute position of every token;
+ * tokens_per_seq consecutive tokens belong to one sequence; page_ids [sequences,
+ * pages_per_seq]; freqs [hd/2] fp32 = base^-(2i/hd).  A position whose page is
+ * missing or out of range sets the bounds bit of the status word and is not
+ * written. */
+int b200moe_attn_rope_kv_write(void* q, const void* k, const void* v, void* k_out, void* v_out, int io_dtype,
+                               void* slab, int cache_dtype, const b200moe_kv_cache_t* cache,
+                               int32_t block_index, const int32_t* positions, const int32_t* page_ids,
+                               const float* freqs, int32_t tokens, int32_t tokens_per_seq,
+                               int32_t pages_per_seq, int32_t heads, void* stream);
+
+/* One decode step of attention over the paged cache: replaces PagedKVCache.read
+ * into a linear temporary (layers/kv_cache.py:351-426), the GQA expansion, the
+ * decomposed matmul / softcap / mask / fp32 softmax / matmul
+ * (paged_llama_attention_block.py:176-214).  K and V rows are read from the pages
+ * through page_ids; positions at or beyond seq_lens[seq] are not attended (what
+ * the reference's decode mask expresses).  q, out: [bs, heads, hd]; softcap <= 0
+ * means none; scratch of b200moe_attn_decode_scratch_bytes(...) bytes holds the
+ * partial results of the position splits.  head_dim 64 or 128, heads / kv_heads
+ * at most 8. */
+size_t b200moe_attn_decode_scratch_bytes(const b200moe_kv_cache_t* cache, int32_t bs, int32_t heads,
+                                         int32_t max_seq_len);
+int b200moe_attn_decode(const void* q, int q_dtype, const void* slab, int cache_dtype,
+                        const b200moe_kv_cache_t* cache, int32_t block_index, const int32_t* page_ids,
+                        const int32_t* seq_lens, int32_t bs, int32_t pages_per_seq, int32_t heads,
+                        int32_t max_seq_len, float scale, float softcap, void* out, int out_dtype,
+                        void* scratch, size_t scratch_bytes, void* stream);
+
 /* A stream of batches from host memory (no reference counterpart: the
  * reference's eager layer takes whatever device its tensors are on).  The
  * pipeline keeps `depth` steps in flight: the host->device copy of a step's

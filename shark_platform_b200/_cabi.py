@@ -55,6 +55,16 @@ class LayerDesc(ctypes.Structure):
     ]
 
 
+class KvCacheDesc(ctypes.Structure):
+    _fields_ = [
+        ("blocks", c_int32),
+        ("stride", c_int32),
+        ("kv_heads", c_int32),
+        ("head_dim", c_int32),
+        ("page_count", c_int32),
+    ]
+
+
 class EpDesc(ctypes.Structure):
     _fields_ = [
         ("world", c_int32),
@@ -120,6 +130,12 @@ _PROTOS = {
     "b200moe_workspace_bytes": (c_size_t, [_L, c_int32]),
     "b200moe_layer_forward": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, c_size_t, _P, _P, _P]),
     "b200moe_layer_forward_host": (c_int, [_L, _P, _P, c_int, c_int32, c_int, _P, _P, c_size_t, _P]),
+    "b200moe_rms_norm": (c_int, [_P, c_int, _P, c_int64, c_int32, c_float, _P, c_int, _P]),
+    "b200moe_attn_rope_kv_write": (c_int, [_P, _P, _P, _P, _P, c_int, _P, c_int, POINTER(KvCacheDesc), c_int32, _P, _P,
+                                           _P, c_int32, c_int32, c_int32, c_int32, _P]),
+    "b200moe_attn_decode_scratch_bytes": (c_size_t, [POINTER(KvCacheDesc), c_int32, c_int32, c_int32]),
+    "b200moe_attn_decode": (c_int, [_P, c_int, _P, c_int, POINTER(KvCacheDesc), c_int32, _P, _P, c_int32, c_int32,
+                                    c_int32, c_int32, c_float, c_float, _P, c_int, _P, c_size_t, _P]),
     "b200moe_pipeline_bytes": (c_size_t, [_L, c_int, c_int32, c_int32]),
     "b200moe_pipeline_create": (c_int, [_L, c_int, c_int32, c_int, c_int32, _P, c_size_t, POINTER(c_void_p)]),
     "b200moe_pipeline_submit": (c_int, [_P, _P, _P, c_int32, _P]),

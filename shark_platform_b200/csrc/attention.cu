@@ -1,0 +1,483 @@
+// The attention block that precedes every MoE layer: RMS norm, rotary embedding
+// fused with the paged KV-cache write, and decode attention that reads K and V
+// straight from the cache pages through the page table (no linearised copy).
+//
+// Page slab layout (one row per page):
+//   [transformer block][K | V][position in page][kv head][head dim]
+// i.e. the K (or V) row of one position and kv head is head_dim contiguous
+// elements, and consecutive positions of a page are kv_heads*head_dim apart.
+#include "kernels.h"
+
+namespace b200moe {
+namespace {
+
+__device__ __forceinline__ float ld_elem(const void* p, int dtype, size_t i) {
+  if (dtype == B200MOE_DT_F32) return static_cast<const float*>(p)[i];
+  if (dtype == B200MOE_DT_F16) return __half2float(static_cast<const __half*>(p)[i]);
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void st_elem(void* p, int dtype, size_t i, float v) {
+  if (dtype == B200MOE_DT_F32) static_cast<float*>(p)[i] = v;
+  else if (dtype == B200MOE_DT_F16) static_cast<__half*>(p)[i] = __float2half_rn(v);
+  else static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+inline size_t dt_bytes(int dt) { return dt == B200MOE_DT_F32 ? 4 : 2; }
+
+// ------------------------------------------------------------------ RMS norm
+// y = w * (x * rsqrt(mean(x^2) + eps)), fp32 arithmetic, one CTA per row.
+__global__ void __launch_bounds__(256)
+rms_norm_rows_kernel(const void* __restrict__ x, int x_dtype, const float* __restrict__ w, int d, float eps,
+                     void* __restrict__ y, int y_dtype) {
+  __shared__ float s_red[8];
+  const size_t row = blockIdx.x;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < d; j += 256) {
+    const float v = ld_elem(x, x_dtype, row * d + j);
+    ss = fmaf(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += s_red[i];
+  const float rstd = 1.0f / sqrtf(tot / static_cast<float>(d) + eps);
+  for (int j = threadIdx.x; j < d; j += 256)
+    st_elem(y, y_dtype, row * d + j, w[j] * (ld_elem(x, x_dtype, row * d + j) * rstd));
+}
+
+// ------------------------------------------- rotary embedding + KV page write
+// One CTA per token.  q is rotated in place; k is rotated and, with v, written
+// to its slot of the page the token's position falls in (and, for prefill, to
+// contiguous k_out / v_out so that the attention over the fresh K/V needs no
+// read-back).  Pairs (2i, 2i+1) share the angle position * freq[i].
+struct RopeArgs {
+  void* q;            // [tokens, heads, hd] in/out
+  const void* k;      // [tokens, kv_heads, hd]
+  const void* v;
+  void* k_out;        // NULL or [tokens, kv_heads, hd]
+  void* v_out;
+  int io_dtype;
+  void* slab;
+  int cache_dtype;
+  const int32_t* positions;  // [tokens] absolute position of every token
+  const int32_t* page_ids;   // [bs, pages_per_seq]
+  const float* freqs;        // [hd / 2]
+  int tokens, tokens_per_seq, pages_per_seq, page_count;
+  int heads, kv_heads, hd, stride, blocks, block_index;
+  int32_t* status;
+};
+
+__global__ void __launch_bounds__(128) rope_kv_write_kernel(const RopeArgs a) {
+  const int t = blockIdx.x;
+  const int b = t / a.tokens_per_seq;
+  const int pos = a.positions[t];
+  const int hpairs = a.hd / 2;
+  const int page_slot = pos / a.stride;
+  long long page = -1;
+  if (pos >= 0 && page_slot < a.pages_per_seq) page = a.page_ids[b * a.pages_per_seq + page_slot];
+  if (page < 0 || page >= a.page_count) {
+    if (threadIdx.x == 0) atomicOr(a.status, DEV_ERR_BOUNDS);
+    page = -1;  // rotate q, skip the cache write
+  }
+  const float fpos = static_cast<float>(pos);
+  // q heads
+  for (int i = threadIdx.x; i < a.heads * hpairs; i += 128) {
+    const int hh = i / hpairs, j = i % hpairs;
+    float sn, cs;
+    sincosf(fpos * a.freqs[j], &sn, &cs);
+    const size_t base = (static_cast<size_t>(t) * a.heads + hh) * a.hd + 2 * j;
+    const float re = ld_elem(a.q, a.io_dtype, base), im = ld_elem(a.q, a.io_dtype, base + 1);
+    st_elem(a.q, a.io_dtype, base, re * cs - im * sn);
+    st_elem(a.q, a.io_dtype, base + 1, im * cs + re * sn);
+  }
+  // k (rotated) and v heads
+  const size_t row_elems = static_cast<size_t>(a.kv_heads) * a.hd;
+  const size_t page_elems = static_cast<size_t>(a.blocks) * 2 * a.stride * row_elems;
+  const size_t k_slot = page < 0 ? 0
+                                 : static_cast<size_t>(page) * page_elems +
+                                       ((static_cast<size_t>(a.block_index) * 2 + 0) * a.stride + pos % a.stride) * row_elems;
+  const size_t v_slot = k_slot + static_cast<size_t>(a.stride) * row_elems;
+  for (int i = threadIdx.x; i < a.kv_heads * hpairs; i += 128) {
+    const int hh = i / hpairs, j = i % hpairs;
+    float sn, cs;
+    sincosf(fpos * a.freqs[j], &sn, &cs);
+    const size_t src = (static_cast<size_t>(t) * a.kv_heads + hh) * a.hd + 2 * j;
+    const float re = ld_elem(a.k, a.io_dtype, src), im = ld_elem(a.k, a.io_dtype, src + 1);
+    // rounded to the activation dtype first, as the reference's rotated K is
+    const float kr = re * cs - im * sn, ki = im * cs + re * sn;
+    const float v0 = ld_elem(a.v, a.io_dtype, src), v1 = ld_elem(a.v, a.io_dtype, src + 1);
+    if (a.k_out != nullptr) {
+      st_elem(a.k_out, a.io_dtype, src, kr);
+      st_elem(a.k_out, a.io_dtype, src + 1, ki);
+      st_elem(a.v_out, a.io_dtype, src, v0);
+      st_elem(a.v_out, a.io_dtype, src + 1, v1);
+    }
+    if (page >= 0) {
+      const size_t dst = static_cast<size_t>(hh) * a.hd + 2 * j;
+      float kr_c = kr, ki_c = ki;
+      if (a.io_dtype == B200MOE_DT_BF16) {
+        kr_c = __bfloat162float(__float2bfloat16_rn(kr));
+        ki_c = __bfloat162float(__float2bfloat16_rn(ki));
+      } else if (a.io_dtype == B200MOE_DT_F16) {
+        kr_c = __half2float(__float2half_rn(kr));
+        ki_c = __half2float(__float2half_rn(ki));
+      }
+      st_elem(a.slab, a.cache_dtype, k_slot + dst, kr_c);
+      st_elem(a.slab, a.cache_dtype, k_slot + dst + 1, ki_c);
+      st_elem(a.slab, a.cache_dtype, v_slot + dst, v0);
+      st_elem(a.slab, a.cache_dtype, v_slot + dst + 1, v1);
+    }
+  }
+}
+
+// ------------------------------------------------------- paged decode attention
+// One CTA per (position split, kv head, sequence): the G = heads / kv_heads query
+// heads that share the kv head are processed together, so every K and V row is
+// read once per split.  128 positions per step: thread t scores position t for
+// all G heads (row-wise 16-byte loads of K), the block does the online-softmax
+// update, then thread t accumulates output column d = t % hd over the step's
+// positions (V rows read coalesced).  Splits are merged by a second kernel.
+constexpr int AD_THREADS = 128;
+constexpr int AD_MAXG = 8;
+
+template <typename TC>
+struct CacheVec;  // 16-byte vector of cache elements -> floats
+template <>
+struct CacheVec<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  }
+  __device__ static float one(const float* p) { return *p; }
+};
+template <>
+struct CacheVec<__half> {
+  static constexpr int N = 8;
+  __device__ static void load(const __half* p, float (&v)[8]) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(u32_as_h2(w[i]));
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ static float one(const __half* p) { return __half2float(*p); }
+};
+template <>
+struct CacheVec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ static float one(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+};
+
+struct DecodeArgs {
+  const void* q;      // [bs, heads, hd] rotated
+  int q_dtype;
+  const void* slab;
+  const int32_t* page_ids;  // [bs, pages_per_seq]
+  const int32_t* seq_lens;  // [bs] positions to attend (the new one included)
+  float* partial;     // [bs, kv_heads, splits, G, hd + 2]
+  int bs, heads, kv_heads, hd, stride, blocks, block_index, pages_per_seq, page_count, splits;
+  float scale, softcap;  // softcap <= 0: none
+  int32_t* status;
+};
+
+template <typename TC, int HD>
+__global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArgs a) {
+  constexpr int GROUPS = AD_THREADS / HD;  // position groups in the P.V phase (hd 128: 1, hd 64: 2)
+  __shared__ float s_q[AD_MAXG][HD];
+  __shared__ float s_p[AD_MAXG][AD_THREADS];
+  __shared__ long long s_vrow[AD_THREADS];
+  __shared__ float s_red[AD_MAXG][AD_THREADS / 32];
+  __shared__ float s_m[AD_MAXG], s_l[AD_MAXG], s_alpha[AD_MAXG];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int G = a.heads / a.kv_heads;
+  const int seq_len = a.seq_lens[b];
+  const TC* slab = static_cast<const TC*>(a.slab);
+  const size_t row_elems = static_cast<size_t>(a.kv_heads) * HD;
+  const size_t page_elems = static_cast<size_t>(a.blocks) * 2 * a.stride * row_elems;
+
+  for (int i = t; i < G * HD; i += AD_THREADS) {
+    const int g = i / HD, d = i % HD;
+    s_q[g][d] = ld_elem(a.q, a.q_dtype, (static_cast<size_t>(b) * a.heads + kvh * G + g) * HD + d) * a.scale;
+  }
+  if (t < AD_MAXG) { s_m[t] = -INFINITY; s_l[t] = 0.f; }
+  __syncthreads();
+
+  // positions of this split, in whole steps of 128
+  const int steps_total = (seq_len + AD_THREADS - 1) / AD_THREADS;
+  const int steps_per = (steps_total + a.splits - 1) / a.splits;
+  const int p_begin = split * steps_per * AD_THREADS;
+  const int p_end = min(seq_len, (split + 1) * steps_per * AD_THREADS);
+
+  const int d_own = t % HD, grp = t / HD;
+  float acc[AD_MAXG];
+#pragma unroll
+  for (int g = 0; g < AD_MAXG; ++g) acc[g] = 0.f;
+
+  for (int p0 = p_begin; p0 < p_end; p0 += AD_THREADS) {
+    const int pos = p0 + t;
+    const bool valid = pos < p_end;
+    float sc[AD_MAXG];
+#pragma unroll
+    for (int g = 0; g < AD_MAXG; ++g) sc[g] = -INFINITY;
+    long long vrow = -1;
+    if (valid) {
+      const int slot = pos / a.stride;
+      long long page = slot < a.pages_per_seq ? a.page_ids[b * a.pages_per_seq + slot] : -1;
+      if (page < 0 || page >= a.page_count) {
+        atomicOr(a.status, DEV_ERR_BOUNDS);
+      } else {
+        const size_t krow = static_cast<size_t>(page) * page_elems +
+                            ((static_cast<size_t>(a.block_index) * 2) * a.stride + pos % a.stride) * row_elems +
+                            static_cast<size_t>(kvh) * HD;
+        vrow = static_cast<long long>(krow + static_cast<size_t>(a.stride) * row_elems);
+        float dot[AD_MAXG];
+#pragma unroll
+        for (int g = 0; g < AD_MAXG; ++g) dot[g] = 0.f;
+        constexpr int N = CacheVec<TC>::N;
+#pragma unroll 4
+        for (int c = 0; c < HD / N; ++c) {
+          float kv[N];
+          CacheVec<TC>::load(slab + krow + c * N, kv);
+#pragma unroll
+          for (int g = 0; g < AD_MAXG; ++g) {
+            if (g < G) {
+#pragma unroll
+              for (int i = 0; i < N; ++i) dot[g] = fmaf(kv[i], s_q[g][c * N + i], dot[g]);
+            }
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < AD_MAXG; ++g) {
+          if (g < G) sc[g] = a.softcap > 0.f ? a.softcap * tanhf(dot[g] / a.softcap) : dot[g];
+        }
+      }
+    }
+    s_vrow[t] = vrow;
+    // block maximum per head
+#pragma unroll
+    for (int g = 0; g < AD_MAXG; ++g) {
+      if (g < G) {
+        float m = sc[g];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) s_red[g][warp] = m;
+      }
+    }
+    __syncthreads();
+    if (t < G) {
+      float m = s_m[t];
+      for (int w = 0; w < AD_THREADS / 32; ++w) m = fmaxf(m, s_red[t][w]);
+      s_alpha[t] = (m == -INFINITY) ? 1.f : __expf(s_m[t] - m);  // exp(-inf) = 0 on the first step
+      s_m[t] = m;
+    }
+    __syncthreads();
+    // probabilities and their block sum
+#pragma unroll
+    for (int g = 0; g < AD_MAXG; ++g) {
+      if (g < G) {
+        const float p = (sc[g] == -INFINITY) ? 0.f : __expf(sc[g] - s_m[g]);
+        s_p[g][t] = p;
+        float s = p;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) s_red[g][warp] = s;
+      }
+    }
+    __syncthreads();
+    if (t < G) {
+      float s = 0.f;
+      for (int w = 0; w < AD_THREADS / 32; ++w) s += s_red[t][w];
+      s_l[t] = s_l[t] * s_alpha[t] + s;
+    }
+    // P.V: thread owns column d_own for the positions j = grp, grp + GROUPS, ...
+#pragma unroll
+    for (int g = 0; g < AD_MAXG; ++g)
+      if (g < G) acc[g] *= s_alpha[g];
+    const int n_here = min(AD_THREADS, p_end - p0);
+    for (int j = grp; j < n_here; j += GROUPS) {
+      const long long vr = s_vrow[j];
+      if (vr < 0) continue;
+      const float v = CacheVec<TC>::one(slab + vr + d_own);
+#pragma unroll
+      for (int g = 0; g < AD_MAXG; ++g)
+        if (g < G) acc[g] = fmaf(s_p[g][j], v, acc[g]);
+    }
+    __syncthreads();  // s_p, s_vrow, s_alpha are rewritten by the next step
+  }
+
+  // merge the position groups, write this split's partial (unnormalised sums, max, denominator)
+  float* out = a.partial + ((static_cast<size_t>(b) * a.kv_heads + kvh) * a.splits + split) * G * (HD + 2);
+  if constexpr (GROUPS > 1) {
+    for (int g = 0; g < G; ++g) {
+      __syncthreads();
+      s_p[0][t] = acc[g];
+      __syncthreads();
+      if (grp == 0) {
+        float s = 0.f;
+        for (int q = 0; q < GROUPS; ++q) s += s_p[0][q * HD + d_own];
+        out[g * (HD + 2) + d_own] = s;
+      }
+    }
+  } else {
+    for (int g = 0; g < G; ++g) out[g * (HD + 2) + d_own] = acc[g];
+  }
+  if (t < G) {
+    out[t * (HD + 2) + HD] = s_m[t];
+    out[t * (HD + 2) + HD + 1] = s_l[t];
+  }
+}
+
+// Merges the splits: out[b, head, d] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M).
+__global__ void __launch_bounds__(128)
+attn_decode_merge_kernel(const float* __restrict__ partial, int splits, int G, int hd, int heads, int kv_heads,
+                         void* __restrict__ out, int out_dtype) {
+  const int head = blockIdx.x, b = blockIdx.y;
+  const int kvh = head / G, g = head % G;
+  const float* base = partial + ((static_cast<size_t>(b) * kv_heads + kvh) * splits) * G * (hd + 2) + g * (hd + 2);
+  const size_t sstride = static_cast<size_t>(G) * (hd + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, base[s * sstride + hd]);
+  float L = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float m = base[s * sstride + hd];
+    if (m != -INFINITY) L += base[s * sstride + hd + 1] * __expf(m - M);
+  }
+  for (int d = threadIdx.x; d < hd; d += 128) {
+    float o = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float m = base[s * sstride + hd];
+      if (m != -INFINITY) o += base[s * sstride + d] * __expf(m - M);
+    }
+    st_elem(out, out_dtype, (static_cast<size_t>(b) * heads + head) * hd + d, L > 0.f ? o / L : 0.f);
+  }
+}
+
+int decode_splits(int bs, int kv_heads, int max_seq_len) {
+  // enough CTAs for two per SM, but no split shorter than 256 positions
+  const int base = bs * kv_heads;
+  int splits = (2 * sm_count() + base - 1) / base;
+  const int most = (max_seq_len + 255) / 256;
+  if (splits > most) splits = most;
+  if (splits < 1) splits = 1;
+  if (splits > 64) splits = 64;
+  return splits;
+}
+
+bool dtype_ok(int dt) { return dt == B200MOE_DT_F32 || dt == B200MOE_DT_F16 || dt == B200MOE_DT_BF16; }
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" {
+
+int b200moe_rms_norm(const void* x, int x_dtype, const float* weight, int64_t rows, int32_t d, float eps,
+                     void* y, int y_dtype, void* stream) {
+  B200_REQUIRE(rows >= 0 && d > 0, "rms_norm: bad sizes");
+  if (rows == 0) return B200MOE_OK;
+  B200_REQUIRE(x && weight && y && dtype_ok(x_dtype) && dtype_ok(y_dtype), "rms_norm: bad argument");
+  rms_norm_rows_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, x_dtype, weight, d, eps, y, y_dtype);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_attn_rope_kv_write(void* q, const void* k, const void* v, void* k_out, void* v_out, int io_dtype,
+                               void* slab, int cache_dtype, const b200moe_kv_cache_t* cache,
+                               int32_t block_index, const int32_t* positions, const int32_t* page_ids,
+                               const float* freqs, int32_t tokens, int32_t tokens_per_seq,
+                               int32_t pages_per_seq, int32_t heads, void* stream) {
+  B200_REQUIRE(cache != nullptr, "attn_rope_kv_write: NULL cache geometry");
+  B200_REQUIRE(tokens >= 0 && tokens_per_seq >= 1 && pages_per_seq >= 1 && heads >= 1, "attn_rope_kv_write: bad sizes");
+  if (tokens == 0) return B200MOE_OK;
+  B200_REQUIRE(q && k && v && slab && positions && page_ids && freqs, "attn_rope_kv_write: NULL buffer");
+  B200_REQUIRE((k_out == nullptr) == (v_out == nullptr), "attn_rope_kv_write: k_out and v_out go together");
+  B200_REQUIRE(dtype_ok(io_dtype) && dtype_ok(cache_dtype), "attn_rope_kv_write: unknown dtype");
+  B200_REQUIRE(cache->head_dim % 2 == 0 && cache->kv_heads >= 1 && cache->stride >= 1 && cache->blocks >= 1 &&
+                   block_index >= 0 && block_index < cache->blocks && cache->page_count >= 1,
+               "attn_rope_kv_write: bad cache geometry");
+  B200_REQUIRE(tokens % tokens_per_seq == 0, "attn_rope_kv_write: tokens must be whole sequences");
+  int32_t* status = device_status_ptr();
+  if (status == nullptr) return B200MOE_ERR_CUDA;
+  RopeArgs a;
+  a.q = q; a.k = k; a.v = v; a.k_out = k_out; a.v_out = v_out; a.io_dtype = io_dtype;
+  a.slab = slab; a.cache_dtype = cache_dtype; a.positions = positions; a.page_ids = page_ids; a.freqs = freqs;
+  a.tokens = tokens; a.tokens_per_seq = tokens_per_seq; a.pages_per_seq = pages_per_seq;
+  a.page_count = cache->page_count; a.heads = heads; a.kv_heads = cache->kv_heads; a.hd = cache->head_dim;
+  a.stride = cache->stride; a.blocks = cache->blocks; a.block_index = block_index; a.status = status;
+  rope_kv_write_kernel<<<tokens, 128, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+size_t b200moe_attn_decode_scratch_bytes(const b200moe_kv_cache_t* cache, int32_t bs, int32_t heads,
+                                         int32_t max_seq_len) {
+  if (cache == nullptr || bs <= 0 || heads <= 0 || cache->kv_heads <= 0 || heads % cache->kv_heads != 0) return 0;
+  const int splits = decode_splits(bs, cache->kv_heads, max_seq_len);
+  return static_cast<size_t>(bs) * heads * splits * (cache->head_dim + 2) * sizeof(float);
+}
+
+int b200moe_attn_decode(const void* q, int q_dtype, const void* slab, int cache_dtype,
+                        const b200moe_kv_cache_t* cache, int32_t block_index, const int32_t* page_ids,
+                        const int32_t* seq_lens, int32_t bs, int32_t pages_per_seq, int32_t heads,
+                        int32_t max_seq_len, float scale, float softcap, void* out, int out_dtype,
+                        void* scratch, size_t scratch_bytes, void* stream) {
+  B200_REQUIRE(cache != nullptr, "attn_decode: NULL cache geometry");
+  B200_REQUIRE(bs >= 0 && pages_per_seq >= 1 && heads >= 1 && max_seq_len >= 1, "attn_decode: bad sizes");
+  if (bs == 0) return B200MOE_OK;
+  B200_REQUIRE(q && slab && page_ids && seq_lens && out && scratch, "attn_decode: NULL buffer");
+  B200_REQUIRE(dtype_ok(q_dtype) && dtype_ok(cache_dtype) && dtype_ok(out_dtype), "attn_decode: unknown dtype");
+  B200_REQUIRE(cache->kv_heads >= 1 && heads % cache->kv_heads == 0 && heads / cache->kv_heads <= AD_MAXG,
+               "attn_decode: heads (%d) must be 1..8 times the kv heads (%d)", heads, cache->kv_heads);
+  B200_REQUIRE(cache->head_dim == 64 || cache->head_dim == 128, "attn_decode: head_dim %d (64 and 128 are built)",
+               cache->head_dim);
+  B200_REQUIRE(block_index >= 0 && block_index < cache->blocks && cache->stride >= 1, "attn_decode: bad block index");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(slab) & 15) == 0, "attn_decode: page slab must be 16-byte aligned");
+  const size_t need = b200moe_attn_decode_scratch_bytes(cache, bs, heads, max_seq_len);
+  if (scratch_bytes < need) {
+    set_error("attn_decode: scratch needs %zu bytes, got %zu", need, scratch_bytes);
+    return B200MOE_ERR_WORKSPACE;
+  }
+  int32_t* status = device_status_ptr();
+  if (status == nullptr) return B200MOE_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DecodeArgs a;
+  a.q = q; a.q_dtype = q_dtype; a.slab = slab; a.page_ids = page_ids; a.seq_lens = seq_lens;
+  a.partial = static_cast<float*>(scratch);
+  a.bs = bs; a.heads = heads; a.kv_heads = cache->kv_heads; a.hd = cache->head_dim; a.stride = cache->stride;
+  a.blocks = cache->blocks; a.block_index = block_index; a.pages_per_seq = pages_per_seq;
+  a.page_count = cache->page_count; a.splits = decode_splits(bs, cache->kv_heads, max_seq_len);
+  a.scale = scale; a.softcap = softcap; a.status = status;
+  const dim3 grid(a.splits, a.kv_heads, bs);
+  const int hd = cache->head_dim;
+#define B200_LAUNCH_DECODE(TC)                                              \
+  if (hd == 64) attn_decode_kernel<TC, 64><<<grid, AD_THREADS, 0, st>>>(a); \
+  else attn_decode_kernel<TC, 128><<<grid, AD_THREADS, 0, st>>>(a);
+  if (cache_dtype == B200MOE_DT_F32) { B200_LAUNCH_DECODE(float) }
+  else if (cache_dtype == B200MOE_DT_F16) { B200_LAUNCH_DECODE(__half) }
+  else { B200_LAUNCH_DECODE(__nv_bfloat16) }
+#undef B200_LAUNCH_DECODE
+  B200_CHECK_CUDA(cudaGetLastError());
+  attn_decode_merge_kernel<<<dim3(heads, bs), 128, 0, st>>>(a.partial, a.splits, heads / cache->kv_heads, hd, heads,
+                                                            cache->kv_heads, out, out_dtype);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+}  // extern "C"

@@ -127,3 +127,16 @@ def test_mixtral_model_with_every_moe_block_swapped(kind):
     for b, n in enumerate(seq_lens.tolist()):
         assert int(got_p[b, n - 1].argmax()) == int(want_p[b, n - 1].argmax())
     assert torch.equal(got_d.argmax(-1), want_d.argmax(-1))
+
+    # the attention blocks as well: rotary + paged-KV write and the paged decode
+    # attention from this library, projections and prefill core from torch
+    from shark_platform_b200 import attention
+
+    assert attention.patch_attention_blocks(model) == BLOCKS
+    assert all(isinstance(b, attention.B200PagedAttentionBlock) for b in model.attn_blocks)
+    got_p2, got_d2, _ = _prefill_and_decode(model, "cuda:0")
+    assert moe.device_status() == 0
+    for b, n in enumerate(seq_lens.tolist()):
+        assert orc.rel_l2(got_p2[b, :n], want_p[b, :n]) < 2e-2
+    assert orc.rel_l2(got_d2, want_d) < 2e-2
+    assert torch.equal(got_d2.argmax(-1), want_d.argmax(-1))
