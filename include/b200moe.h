@@ -150,7 +150,9 @@ int b200moe_route_plan(const int32_t* experts, int32_t pairs, int32_t expert_beg
  * whether the shape qualifies (at most 128 tokens, hidden <= 8192 and a
  * multiple of 256).  No reference counterpart: the reference runs these steps
  * as separate torch operators (layers/mixture_of_experts_block.py:66-83,
- * layers/ffn_moe_block.py:37-41). */
+ * layers/ffn_moe_block.py:37-41).  The launch takes one of 32 grid-barrier
+ * slots per device in rotation; that host-side rotation is not synchronised
+ * between threads: one thread per device issues these calls. */
 int b200moe_front_supported(int32_t tokens, const b200moe_layer_t* layer);
 int b200moe_front(const void* h, int h_dtype, int32_t tokens, const b200moe_layer_t* layer,
                   int kperm, int32_t* experts_out, float* gates_out, int32_t* counts,

@@ -193,10 +193,14 @@ __device__ __forceinline__ void dequant_q8x4(uint32_t w, __half2 scale, uint32_t
 // Eight 4-bit quants of one 32-bit word (k order: nibble i of byte b is
 // element 2b+i) -> fp16(fp16(ds*q) - dm) as four half2 whose element pairs are
 // (q0,q4) (q1,q5) (q2,q6) (q3,q7): the pair order the activation rows are
-// pre-permuted to.  0x6400|q is 1024+q exactly, so one subtraction gives q.
+// pre-permuted to.  0x6400|q is the fp16 number 1024+q, and -1024*ds is exact in
+// fp16 (a power-of-two multiple; ds < 64), so one fused multiply-add
+// (1024+q)*ds - 1024*ds is the exact product ds*q rounded once — the value of the
+// reference's fp16 multiply — without first subtracting the 1024.  The offset is
+// then subtracted with its own rounding (_rn: never contracted into the fma).
 __device__ __forceinline__ void dequant_q4x8(uint32_t w, __half2 ds, __half2 dm,
                                              uint32_t (&out)[4]) {
-  const __half2 k1024 = u32_as_h2(0x64006400u);
+  const __half2 nds1024 = __hmul2(ds, u32_as_h2(0xE400E400u));  // -1024 * ds, exact
   const uint32_t w1 = w >> 8;
   uint32_t e[4];
   e[0] = (w & 0x000f000fu) | 0x64006400u;          // (q0, q4)
@@ -205,8 +209,8 @@ __device__ __forceinline__ void dequant_q4x8(uint32_t w, __half2 ds, __half2 dm,
   e[3] = ((w1 >> 4) & 0x000f000fu) | 0x64006400u;  // (q3, q7)
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const __half2 q = __hsub2(u32_as_h2(e[i]), k1024);
-    out[i] = h2_as_u32(__hsub2_rn(__hmul2_rn(ds, q), dm));  // _rn: no fma contraction
+    const __half2 t = __hfma2(u32_as_h2(e[i]), ds, nds1024);
+    out[i] = h2_as_u32(__hsub2_rn(t, dm));
   }
 }
 

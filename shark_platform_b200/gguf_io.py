@@ -179,28 +179,35 @@ def _scalar(v):
 
 
 def load_properties(reader) -> dict:
-    """The file's key/value fields as Python scalars, strings and lists
-    (base.py:64-83); always carries "schema": "GGUF"."""
+    """The file's key/value metadata as plain Python values (what base.py:64-83
+    extracts): strings, numbers, and flat lists of either, plus "schema": "GGUF".
+    A scalar of a type the reader has no numpy mapping for is left out; nested or
+    otherwise undecodable arrays are an error."""
     from gguf import GGUFValueType
 
+    def element_decoder(kind):
+        if kind == GGUFValueType.STRING:
+            return lambda part: bytes(part).decode("utf8")
+        if kind in reader.gguf_scalar_to_np:
+            return lambda part: _scalar(part[0])
+        return None
+
     props: dict[str, Any] = {"schema": "GGUF"}
-    for f in reader.fields.values():
-        if len(f.types) == 1:
-            if f.types[0] == GGUFValueType.STRING:
-                props[f.name] = str(bytes(f.parts[-1]), encoding="utf8")
-            elif f.types[0] in reader.gguf_scalar_to_np:
-                props[f.name] = _scalar(f.parts[-1][0])
-        elif f.types[0] == GGUFValueType.ARRAY:
-            if len(f.types) != 2:
-                raise ValueError(f"Unsupported array type {f.types}")
-            if f.types[1] == GGUFValueType.STRING:
-                props[f.name] = [str(bytes(f.parts[i]), encoding="utf8") for i in f.data]
-            elif f.types[1] in reader.gguf_scalar_to_np:
-                props[f.name] = [_scalar(f.parts[i][0]) for i in f.data]
-            else:
-                raise ValueError(f"Unsupported array element type {f.types[1]}")
-        else:
-            raise ValueError("Invalid field type.")
+    for field in reader.fields.values():
+        kinds = list(field.types)
+        if not kinds:
+            raise ValueError(f"GGUF field {field.name!r} carries no value type")
+        if kinds[0] != GGUFValueType.ARRAY:
+            if len(kinds) != 1:
+                raise ValueError(f"GGUF field {field.name!r}: unexpected type chain {kinds}")
+            decode = element_decoder(kinds[0])
+            if decode is not None:
+                props[field.name] = decode(field.parts[-1])
+            continue
+        decode = element_decoder(kinds[1]) if len(kinds) == 2 else None
+        if decode is None:
+            raise ValueError(f"GGUF field {field.name!r}: arrays of {kinds[1:]} cannot be decoded")
+        props[field.name] = [decode(field.parts[i]) for i in field.data]
     return props
 
 
@@ -218,9 +225,10 @@ def wrap_tensor(name: str, ggml_shape: list[int], type_name: str, data, device="
         return T.DefaultPrimitiveTensor(
             name=name, data=torch.from_numpy(arr.copy()).view(torch.bfloat16).to(device))
     cls = _QUANTIZED.get(type_name)
-    if cls is not None:
-        return cls(name=name, raw=data, shape=shape, device=device)
-    raise ValueError(f"Unsupported gguf tensor type: {type_name}")
+    if cls is None:
+        raise ValueError(f"tensor {name!r}: GGUF type {type_name} has no layout here "
+                         f"(dense {sorted(_DENSE)} + BF16, quantized {sorted(_QUANTIZED)})")
+    return cls(name=name, raw=data, shape=shape, device=device)
 
 
 def load_file(gguf_path: Union[str, os.PathLike], device="cuda") -> Dataset:
