@@ -14,6 +14,9 @@ SiLU, Q8_0 weights, bf16 activations, seeded synthetic values unless noted):
   grok_prefill8192                 Grok-1 shape (hidden 6144, ffn 32768, GELU, output norm)
   stack32_decode64                 32 Mixtral layers back to back, 64 tokens, Zipf(1.2)
                                    router bias per layer (weights drawn on the device)
+  attn_decode                      the attention block's paged decode kernel alone, Mixtral
+                                   shape (32 heads, 8 kv heads, head_dim 128), 32 sequences
+                                   of 4096 cached positions, fp16 cache (HBM bound)
   profile_small                    the Mixtral layer with a quarter of the ffn rows (3584;
                                    374 MB of Q8_0 weights, larger than L2) for profiler
                                    captures: --tokens sets the token count, --regime the
@@ -57,6 +60,7 @@ WORKLOADS = {
     "grok_prefill8192": ("grok_q8", 8192),
     "stack32_decode64": ("mixtral_q8", 64),
     "profile_small": ("mixtral_q8", 256),
+    "attn_decode": ("mixtral_q8", 32),
 }
 STAGES = ["router", "route_plan", "permute", "gate_up", "down", "combine"]
 SOAK_S = 0.6          # same load before the timed region, so that it runs at the settled clock
@@ -435,6 +439,47 @@ def main():
     peaks = measured_peaks()
     spec = syn.CASES[spec_name]
     transport = args.ep
+
+    # ------------------------------------------ decode attention over the pages
+    if args.workload == "attn_decode":
+        bs, seq, heads, kvh, hd, stride, blocks = 32, args.tokens or 4096, 32, 8, 128, 32, 1
+        per = seq // stride + 1
+        pages = bs * per
+        desc = C.KvCacheDesc(blocks, stride, kvh, hd, pages)
+        gen = torch.Generator(device=dev).manual_seed(7)
+        slab = (torch.randn(pages, blocks * 2 * stride * kvh * hd, generator=gen, device=dev) * 0.5).half()
+        q = torch.randn(bs, heads, hd, generator=gen, device=dev).half()
+        ids = torch.randperm(pages, generator=gen, device=dev).to(torch.int32).view(bs, per)
+        lens = torch.full((bs,), seq, dtype=torch.int32, device=dev)
+        out = torch.empty_like(q)
+        nbytes = C.lib.b200moe_attn_decode_scratch_bytes(ctypes.byref(desc), bs, heads, per * stride)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        pp = lambda t: ctypes.c_void_p(t.data_ptr())
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+        def step():
+            C.check(C.lib.b200moe_attn_decode(pp(q), C.DT_F16, pp(slab), C.DT_F16, ctypes.byref(desc), 0, pp(ids),
+                                              pp(lens), bs, per, heads, per * stride, 1.0 / hd ** 0.5, 0.0, pp(out),
+                                              C.DT_F16, pp(scratch), nbytes, st), "attn_decode")
+
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        soak(step, 0.3)
+        ms = event_ms(step, args.steps) / args.steps
+        moe.device_status()
+        kv_bytes = bs * seq * kvh * hd * 2 * 2
+        ach = kv_bytes / (ms * 1e-3) / 1e9
+        print(json.dumps({"metric": "attention_decode_tokens_per_s", "value": bs / (ms * 1e-3), "unit": "tokens/s",
+                          "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                          "higher_is_better": True, "data": "synthetic", "dtype": "f16 cache, f32 softmax",
+                          "config": {"workload": "attn_decode", "sequences": bs, "cached_positions": seq,
+                                     "heads": heads, "kv_heads": kvh, "head_dim": hd, "page_stride": stride},
+                          "roofline": {"bound": "hbm", "kernel": "attn_decode", "achieved": ach,
+                                       "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                                       "traffic": None, "algorithmic_bytes": kv_bytes,
+                                       "peak_source": peaks["source"] + " (copy)"}}), flush=True)
+        return
 
     # ------------------------------------------------------------ profiler case
     if args.workload == "profile_small":

@@ -135,10 +135,17 @@ __global__ void __launch_bounds__(128) rope_kv_write_kernel(const RopeArgs a) {
 // ------------------------------------------------------- paged decode attention
 // One CTA per (position split, kv head, sequence): the G = heads / kv_heads query
 // heads that share the kv head are processed together, so every K and V row is
-// read once per split.  128 positions per step: thread t scores position t for
-// all G heads (row-wise 16-byte loads of K), the block does the online-softmax
-// update, then thread t accumulates output column d = t % hd over the step's
-// positions (V rows read coalesced).  Splits are merged by a second kernel.
+// read once per split.  Per step of 128 positions:
+//   1. the K rows and the V rows of the step are copied into shared memory with
+//      cp.async (16 bytes per lane, a row's bytes by consecutive lanes: fully
+//      coalesced; V's copy stays in flight during 2 and 3);
+//   2. thread t scores position t for all G heads from its shared-memory row
+//      (rows are padded by 16 bytes so that 16-byte row reads of a quarter warp
+//      hit all 32 banks);
+//   3. block-wide online-softmax update;
+//   4. thread t accumulates output column d = t % hd over the step's positions
+//      from the V tile.
+// Splits are merged by a second kernel.
 constexpr int AD_THREADS = 128;
 constexpr int AD_MAXG = 8;
 
@@ -194,14 +201,27 @@ struct DecodeArgs {
   int32_t* status;
 };
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <typename TC, int HD>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArgs a) {
-  constexpr int GROUPS = AD_THREADS / HD;  // position groups in the P.V phase (hd 128: 1, hd 64: 2)
+  constexpr int GROUPS = AD_THREADS / HD;        // position groups in the P.V phase (hd 128: 1, hd 64: 2)
+  constexpr int ROW_B = HD * sizeof(TC);         // bytes of one K or V row
+  constexpr int ROW_PAD = ROW_B + 16;            // shared-memory row pitch
+  constexpr int CHUNKS = ROW_B / 16;             // 16-byte pieces per row
+  extern __shared__ __align__(16) uint8_t s_tiles[];  // K tile, then V tile: 2 x 128 x ROW_PAD
   __shared__ float s_q[AD_MAXG][HD];
   __shared__ float s_p[AD_MAXG][AD_THREADS];
-  __shared__ long long s_vrow[AD_THREADS];
+  __shared__ long long s_row[AD_THREADS];        // element offset of each position's K row, -1 = none
   __shared__ float s_red[AD_MAXG][AD_THREADS / 32];
   __shared__ float s_m[AD_MAXG], s_l[AD_MAXG], s_alpha[AD_MAXG];
+  uint8_t* s_k = s_tiles;
+  uint8_t* s_v = s_tiles + AD_THREADS * ROW_PAD;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int G = a.heads / a.kv_heads;
@@ -209,13 +229,13 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArg
   const TC* slab = static_cast<const TC*>(a.slab);
   const size_t row_elems = static_cast<size_t>(a.kv_heads) * HD;
   const size_t page_elems = static_cast<size_t>(a.blocks) * 2 * a.stride * row_elems;
+  const size_t v_off = static_cast<size_t>(a.stride) * row_elems;  // V row = K row + this many elements
 
   for (int i = t; i < G * HD; i += AD_THREADS) {
     const int g = i / HD, d = i % HD;
     s_q[g][d] = ld_elem(a.q, a.q_dtype, (static_cast<size_t>(b) * a.heads + kvh * G + g) * HD + d) * a.scale;
   }
   if (t < AD_MAXG) { s_m[t] = -INFINITY; s_l[t] = 0.f; }
-  __syncthreads();
 
   // positions of this split, in whole steps of 128
   const int steps_total = (seq_len + AD_THREADS - 1) / AD_THREADS;
@@ -229,45 +249,66 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArg
   for (int g = 0; g < AD_MAXG; ++g) acc[g] = 0.f;
 
   for (int p0 = p_begin; p0 < p_end; p0 += AD_THREADS) {
-    const int pos = p0 + t;
-    const bool valid = pos < p_end;
+    const int n_here = min(AD_THREADS, p_end - p0);
+    // row offsets of the step's positions
+    {
+      const int pos = p0 + t;
+      long long row = -1;
+      if (t < n_here) {
+        const int slot = pos / a.stride;
+        const long long page = slot < a.pages_per_seq ? a.page_ids[b * a.pages_per_seq + slot] : -1;
+        if (page < 0 || page >= a.page_count) {
+          atomicOr(a.status, DEV_ERR_BOUNDS);
+        } else {
+          row = static_cast<long long>(static_cast<size_t>(page) * page_elems +
+                                       ((static_cast<size_t>(a.block_index) * 2) * a.stride + pos % a.stride) * row_elems +
+                                       static_cast<size_t>(kvh) * HD);
+        }
+      }
+      s_row[t] = row;
+    }
+    __syncthreads();
+    // K tile, then V tile, 16 bytes per lane per copy
+    for (int i = t; i < n_here * CHUNKS; i += AD_THREADS) {
+      const int r = i / CHUNKS, c = i % CHUNKS;
+      const long long row = s_row[r];
+      if (row >= 0) cp_async16(smem_u32(s_k + r * ROW_PAD + c * 16), slab + row + c * (16 / sizeof(TC)));
+    }
+    cp_async_commit();
+    for (int i = t; i < n_here * CHUNKS; i += AD_THREADS) {
+      const int r = i / CHUNKS, c = i % CHUNKS;
+      const long long row = s_row[r];
+      if (row >= 0) cp_async16(smem_u32(s_v + r * ROW_PAD + c * 16), slab + row + v_off + c * (16 / sizeof(TC)));
+    }
+    cp_async_commit();
+    cp_async_wait<1>();  // K has landed (this thread's copies)
+    __syncthreads();     // everyone's
     float sc[AD_MAXG];
 #pragma unroll
     for (int g = 0; g < AD_MAXG; ++g) sc[g] = -INFINITY;
-    long long vrow = -1;
-    if (valid) {
-      const int slot = pos / a.stride;
-      long long page = slot < a.pages_per_seq ? a.page_ids[b * a.pages_per_seq + slot] : -1;
-      if (page < 0 || page >= a.page_count) {
-        atomicOr(a.status, DEV_ERR_BOUNDS);
-      } else {
-        const size_t krow = static_cast<size_t>(page) * page_elems +
-                            ((static_cast<size_t>(a.block_index) * 2) * a.stride + pos % a.stride) * row_elems +
-                            static_cast<size_t>(kvh) * HD;
-        vrow = static_cast<long long>(krow + static_cast<size_t>(a.stride) * row_elems);
-        float dot[AD_MAXG];
+    if (t < n_here && s_row[t] >= 0) {
+      float dot[AD_MAXG];
 #pragma unroll
-        for (int g = 0; g < AD_MAXG; ++g) dot[g] = 0.f;
-        constexpr int N = CacheVec<TC>::N;
+      for (int g = 0; g < AD_MAXG; ++g) dot[g] = 0.f;
+      constexpr int N = CacheVec<TC>::N;
+      const TC* krow = reinterpret_cast<const TC*>(s_k + t * ROW_PAD);
 #pragma unroll 4
-        for (int c = 0; c < HD / N; ++c) {
-          float kv[N];
-          CacheVec<TC>::load(slab + krow + c * N, kv);
-#pragma unroll
-          for (int g = 0; g < AD_MAXG; ++g) {
-            if (g < G) {
-#pragma unroll
-              for (int i = 0; i < N; ++i) dot[g] = fmaf(kv[i], s_q[g][c * N + i], dot[g]);
-            }
-          }
-        }
+      for (int c = 0; c < HD / N; ++c) {
+        float kv[N];
+        CacheVec<TC>::load(krow + c * N, kv);
 #pragma unroll
         for (int g = 0; g < AD_MAXG; ++g) {
-          if (g < G) sc[g] = a.softcap > 0.f ? a.softcap * tanhf(dot[g] / a.softcap) : dot[g];
+          if (g < G) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) dot[g] = fmaf(kv[i], s_q[g][c * N + i], dot[g]);
+          }
         }
       }
+#pragma unroll
+      for (int g = 0; g < AD_MAXG; ++g) {
+        if (g < G) sc[g] = a.softcap > 0.f ? a.softcap * tanhf(dot[g] / a.softcap) : dot[g];
+      }
     }
-    s_vrow[t] = vrow;
     // block maximum per head
 #pragma unroll
     for (int g = 0; g < AD_MAXG; ++g) {
@@ -298,6 +339,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArg
         if (lane == 0) s_red[g][warp] = s;
       }
     }
+    cp_async_wait<0>();  // V has landed
     __syncthreads();
     if (t < G) {
       float s = 0.f;
@@ -308,16 +350,14 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArg
 #pragma unroll
     for (int g = 0; g < AD_MAXG; ++g)
       if (g < G) acc[g] *= s_alpha[g];
-    const int n_here = min(AD_THREADS, p_end - p0);
     for (int j = grp; j < n_here; j += GROUPS) {
-      const long long vr = s_vrow[j];
-      if (vr < 0) continue;
-      const float v = CacheVec<TC>::one(slab + vr + d_own);
+      if (s_row[j] < 0) continue;
+      const float v = CacheVec<TC>::one(reinterpret_cast<const TC*>(s_v + j * ROW_PAD) + d_own);
 #pragma unroll
       for (int g = 0; g < AD_MAXG; ++g)
         if (g < G) acc[g] = fmaf(s_p[g][j], v, acc[g]);
     }
-    __syncthreads();  // s_p, s_vrow, s_alpha are rewritten by the next step
+    __syncthreads();  // s_row, s_p and the tiles are rewritten by the next step
   }
 
   // merge the position groups, write this split's partial (unnormalised sums, max, denominator)
@@ -368,14 +408,32 @@ attn_decode_merge_kernel(const float* __restrict__ partial, int splits, int G, i
 }
 
 int decode_splits(int bs, int kv_heads, int max_seq_len) {
-  // enough CTAs for two per SM, but no split shorter than 256 positions
+  // about six CTAs per SM (each holds 64-130 KB of shared-memory tiles at most
+  // three deep, and the steps of one CTA are serial), but no split shorter than
+  // one 128-position step
   const int base = bs * kv_heads;
-  int splits = (2 * sm_count() + base - 1) / base;
-  const int most = (max_seq_len + 255) / 256;
+  int splits = (6 * sm_count() + base - 1) / base;
+  const int most = (max_seq_len + AD_THREADS - 1) / AD_THREADS;
   if (splits > most) splits = most;
   if (splits < 1) splits = 1;
   if (splits > 64) splits = 64;
   return splits;
+}
+
+template <typename TC, int HD>
+int launch_decode(const DecodeArgs& a, dim3 grid, cudaStream_t st) {
+  constexpr int SMEM = 2 * AD_THREADS * (HD * static_cast<int>(sizeof(TC)) + 16);
+  auto kern = attn_decode_kernel<TC, HD>;
+  static bool configured[16] = {};
+  int dev = 0;
+  B200_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 16 && !configured[dev]) {
+    B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    configured[dev] = true;
+  }
+  kern<<<grid, AD_THREADS, SMEM, st>>>(a);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
 }
 
 bool dtype_ok(int dt) { return dt == B200MOE_DT_F32 || dt == B200MOE_DT_F16 || dt == B200MOE_DT_BF16; }
@@ -466,14 +524,14 @@ int b200moe_attn_decode(const void* q, int q_dtype, const void* slab, int cache_
   a.scale = scale; a.softcap = softcap; a.status = status;
   const dim3 grid(a.splits, a.kv_heads, bs);
   const int hd = cache->head_dim;
-#define B200_LAUNCH_DECODE(TC)                                              \
-  if (hd == 64) attn_decode_kernel<TC, 64><<<grid, AD_THREADS, 0, st>>>(a); \
-  else attn_decode_kernel<TC, 128><<<grid, AD_THREADS, 0, st>>>(a);
-  if (cache_dtype == B200MOE_DT_F32) { B200_LAUNCH_DECODE(float) }
-  else if (cache_dtype == B200MOE_DT_F16) { B200_LAUNCH_DECODE(__half) }
-  else { B200_LAUNCH_DECODE(__nv_bfloat16) }
-#undef B200_LAUNCH_DECODE
-  B200_CHECK_CUDA(cudaGetLastError());
+  int rc;
+  if (cache_dtype == B200MOE_DT_F32)
+    rc = hd == 64 ? launch_decode<float, 64>(a, grid, st) : launch_decode<float, 128>(a, grid, st);
+  else if (cache_dtype == B200MOE_DT_F16)
+    rc = hd == 64 ? launch_decode<__half, 64>(a, grid, st) : launch_decode<__half, 128>(a, grid, st);
+  else
+    rc = hd == 64 ? launch_decode<__nv_bfloat16, 64>(a, grid, st) : launch_decode<__nv_bfloat16, 128>(a, grid, st);
+  if (rc) return rc;
   attn_decode_merge_kernel<<<dim3(heads, bs), 128, 0, st>>>(a.partial, a.splits, heads / cache->kv_heads, hd, heads,
                                                             cache->kv_heads, out, out_dtype);
   B200_CHECK_CUDA(cudaGetLastError());
