@@ -362,19 +362,26 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArg
 
   // merge the position groups, write this split's partial (unnormalised sums, max, denominator)
   float* out = a.partial + ((static_cast<size_t>(b) * a.kv_heads + kvh) * a.splits + split) * G * (HD + 2);
+  // (loops over g are unrolled with a static bound: a dynamically indexed acc[]
+  // would live in local memory for the whole kernel)
   if constexpr (GROUPS > 1) {
-    for (int g = 0; g < G; ++g) {
-      __syncthreads();
-      s_p[0][t] = acc[g];
-      __syncthreads();
-      if (grp == 0) {
-        float s = 0.f;
-        for (int q = 0; q < GROUPS; ++q) s += s_p[0][q * HD + d_own];
-        out[g * (HD + 2) + d_own] = s;
+#pragma unroll
+    for (int g = 0; g < AD_MAXG; ++g) {
+      if (g < G) {
+        __syncthreads();
+        s_p[0][t] = acc[g];
+        __syncthreads();
+        if (grp == 0) {
+          float s = 0.f;
+          for (int q = 0; q < GROUPS; ++q) s += s_p[0][q * HD + d_own];
+          out[g * (HD + 2) + d_own] = s;
+        }
       }
     }
   } else {
-    for (int g = 0; g < G; ++g) out[g * (HD + 2) + d_own] = acc[g];
+#pragma unroll
+    for (int g = 0; g < AD_MAXG; ++g)
+      if (g < G) out[g * (HD + 2) + d_own] = acc[g];
   }
   if (t < G) {
     out[t * (HD + 2) + HD] = s_m[t];
