@@ -389,6 +389,259 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeArg
   }
 }
 
+// ---- the same on tensor cores, for 16-bit caches -----------------------------
+// Scores and outputs as mma.sync.m16n8k16 products with the G query heads as the
+// M dimension (padded to 16):  S[head][pos] = Q[head][:] . K[pos][:]  and
+// O[head][d] = sum_pos P[head][pos] V[pos][d].  The accumulator fragment of S is,
+// element for element, the A fragment of P for the second product, so the
+// probabilities never leave registers.  Four warps per CTA; per stage of 64
+// positions every warp owns 16 of them with its own online-softmax state; the K
+// and V rows of a stage arrive by cp.async (16 bytes per lane, coalesced, rows
+// beyond the sequence zero-filled) into a two-stage ring, rows padded by 16 bytes
+// so that ldmatrix reads are conflict-free.  Per 16 positions a warp issues 32
+// MMAs and 16 ldmatrix for 8 KB of cache: the kernel is left to wait for memory.
+constexpr int ADT_STAGE_POS = 64;
+constexpr int ADT_STAGES = 2;
+
+template <typename TC>
+struct Mma16;
+template <>
+struct Mma16<__half> {
+  __device__ static uint32_t pack(float a, float b) { return h2_as_u32(__floats2half2_rn(a, b)); }
+  __device__ static void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                             uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+template <>
+struct Mma16<__nv_bfloat16> {
+  __device__ static uint32_t pack(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  __device__ static void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                             uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// 16-byte copy, or 16 bytes of zeros when `valid` is false
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+
+template <typename TC, int HD>
+__global__ void __launch_bounds__(AD_THREADS) attn_decode_mma_kernel(const DecodeArgs a) {
+  constexpr int ROW_B = HD * 2;
+  constexpr int ROW_PAD = ROW_B + 16;
+  constexpr int CHUNKS = ROW_B / 16;
+  constexpr int TILE = ADT_STAGE_POS * ROW_PAD;       // one K or V tile of a stage
+  constexpr int KSTEPS = HD / 16, DTILES = HD / 8;
+  extern __shared__ __align__(16) uint8_t s_ring[];   // [stage][K tile | V tile]
+  __shared__ long long s_row[ADT_STAGES][ADT_STAGE_POS];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int G = a.heads / a.kv_heads;
+  const int seq_len = a.seq_lens[b];
+  const TC* slab = static_cast<const TC*>(a.slab);
+  const size_t row_elems = static_cast<size_t>(a.kv_heads) * HD;
+  const size_t page_elems = static_cast<size_t>(a.blocks) * 2 * a.stride * row_elems;
+  const size_t v_off = static_cast<size_t>(a.stride) * row_elems;
+
+  // this split's positions, in whole stages
+  const int stages_total = (seq_len + ADT_STAGE_POS - 1) / ADT_STAGE_POS;
+  const int stages_per = (stages_total + a.splits - 1) / a.splits;
+  const int p_begin = split * stages_per * ADT_STAGE_POS;
+  const int p_end = min(seq_len, (split + 1) * stages_per * ADT_STAGE_POS);
+  const int nstages = p_end > p_begin ? (p_end - p_begin + ADT_STAGE_POS - 1) / ADT_STAGE_POS : 0;
+
+  // Q fragments: rows = heads (gid < G, else zero), scaled
+  uint32_t qa0[KSTEPS], qa2[KSTEPS];
+#pragma unroll
+  for (int s = 0; s < KSTEPS; ++s) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (gid < G) {
+      const size_t base = (static_cast<size_t>(b) * a.heads + kvh * G + gid) * HD + 16 * s + 2 * tig;
+      v[0] = ld_elem(a.q, a.q_dtype, base) * a.scale;
+      v[1] = ld_elem(a.q, a.q_dtype, base + 1) * a.scale;
+      v[2] = ld_elem(a.q, a.q_dtype, base + 8) * a.scale;
+      v[3] = ld_elem(a.q, a.q_dtype, base + 9) * a.scale;
+    }
+    qa0[s] = Mma16<TC>::pack(v[0], v[1]);
+    qa2[s] = Mma16<TC>::pack(v[2], v[3]);
+  }
+
+  auto issue_stage = [&](int st_i) {
+    const int slot = st_i % ADT_STAGES;
+    const int p0 = p_begin + st_i * ADT_STAGE_POS;
+    if (t < ADT_STAGE_POS) {
+      const int pos = p0 + t;
+      long long row = -1;
+      if (pos < p_end) {
+        const int pslot = pos / a.stride;
+        const long long page = pslot < a.pages_per_seq ? a.page_ids[b * a.pages_per_seq + pslot] : -1;
+        if (page < 0 || page >= a.page_count) {
+          atomicOr(a.status, DEV_ERR_BOUNDS);
+        } else {
+          row = static_cast<long long>(static_cast<size_t>(page) * page_elems +
+                                       ((static_cast<size_t>(a.block_index) * 2) * a.stride + pos % a.stride) * row_elems +
+                                       static_cast<size_t>(kvh) * HD);
+        }
+      }
+      s_row[slot][t] = row;
+    }
+    __syncthreads();
+    uint8_t* kt = s_ring + slot * 2 * TILE;
+    uint8_t* vt = kt + TILE;
+    for (int i = t; i < ADT_STAGE_POS * CHUNKS; i += AD_THREADS) {
+      const int r = i / CHUNKS, c = i % CHUNKS;
+      const long long row = s_row[slot][r];
+      const TC* src = slab + (row >= 0 ? row : 0) + c * 8;
+      cp_async16_zfill(smem_u32(kt + r * ROW_PAD + c * 16), src, row >= 0);
+      cp_async16_zfill(smem_u32(vt + r * ROW_PAD + c * 16), src + v_off, row >= 0);
+    }
+    cp_async_commit();
+  };
+
+  float m_run = -INFINITY, l_run = 0.f;  // head gid; l_run is this lane's share (its tig columns)
+  float o[DTILES][2];                    // O[head gid][d = 8*j + 2*tig, +1]
+#pragma unroll
+  for (int j = 0; j < DTILES; ++j) o[j][0] = o[j][1] = 0.f;
+
+  if (nstages > 0) issue_stage(0);
+  for (int st_i = 0; st_i < nstages; ++st_i) {
+    if (st_i + 1 < nstages) {
+      issue_stage(st_i + 1);   // its barrier also says: stage st_i - 1's slot is no longer read
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();           // stage st_i has landed for everyone
+    const int slot = st_i % ADT_STAGES;
+    const uint32_t kt = smem_u32(s_ring + slot * 2 * TILE) + warp * 16 * ROW_PAD;
+    const uint32_t vt = kt + TILE;
+    const int p0 = p_begin + st_i * ADT_STAGE_POS + warp * 16;  // this warp's 16 positions
+
+    // S[head][pos]: two n-tiles of 8 positions
+    float sc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+    {
+      const int mi = lane >> 3, r = lane & 7;  // matrix index and row this lane addresses
+      const uint32_t base = kt + (8 * (mi >> 1) + r) * ROW_PAD + 16 * (mi & 1);
+#pragma unroll
+      for (int s = 0; s < KSTEPS; ++s) {
+        uint32_t kb[4];
+        ldmatrix_x4(base + 32 * s, kb);
+        Mma16<TC>::mma(sc[0], qa0[s], 0u, qa2[s], 0u, kb[0], kb[1]);
+        Mma16<TC>::mma(sc[1], qa0[s], 0u, qa2[s], 0u, kb[2], kb[3]);
+      }
+    }
+    // online softmax for head gid over this lane's four positions, then across the tig lanes
+    float pv[2][2];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float v = sc[j][e];
+        if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+        if (p0 + 8 * j + 2 * tig + e >= p_end) v = -INFINITY;
+        pv[j][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float alpha = (m_new == -INFINITY) ? 1.f : __expf(m_run - m_new);
+    float psum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float p = (pv[j][e] == -INFINITY) ? 0.f : __expf(pv[j][e] - m_new);
+        pv[j][e] = p;
+        psum += p;
+      }
+    m_run = m_new;
+    l_run = l_run * alpha + psum;
+    const uint32_t pa0 = Mma16<TC>::pack(pv[0][0], pv[0][1]);
+    const uint32_t pa2 = Mma16<TC>::pack(pv[1][0], pv[1][1]);
+    // O[head][d] = O * alpha + P . V
+    {
+      const int mi = lane >> 3, r = lane & 7;
+      const uint32_t base = vt + (8 * (mi & 1) + r) * ROW_PAD + 16 * (mi >> 1);
+#pragma unroll
+      for (int j = 0; j < DTILES; j += 2) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(base + 16 * j, vb);
+        float c0[4] = {o[j][0] * alpha, o[j][1] * alpha, 0.f, 0.f};
+        float c1[4] = {o[j + 1][0] * alpha, o[j + 1][1] * alpha, 0.f, 0.f};
+        Mma16<TC>::mma(c0, pa0, 0u, pa2, 0u, vb[0], vb[1]);
+        Mma16<TC>::mma(c1, pa0, 0u, pa2, 0u, vb[2], vb[3]);
+        o[j][0] = c0[0]; o[j][1] = c0[1];
+        o[j + 1][0] = c1[0]; o[j + 1][1] = c1[1];
+      }
+    }
+  }
+  // this lane's share of the denominator -> the head's
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+
+  // merge the four warps (each saw different positions) through shared memory
+  __syncthreads();  // the ring is free
+  float* s_o = reinterpret_cast<float*>(s_ring);            // [warp][G][HD]
+  float* s_ml = s_o + 4 * AD_MAXG * HD;                       // [warp][G][2]
+  if (gid < G) {
+#pragma unroll
+    for (int j = 0; j < DTILES; ++j) {
+      s_o[(warp * AD_MAXG + gid) * HD + 8 * j + 2 * tig] = o[j][0];
+      s_o[(warp * AD_MAXG + gid) * HD + 8 * j + 2 * tig + 1] = o[j][1];
+    }
+    if (tig == 0) {
+      s_ml[(warp * AD_MAXG + gid) * 2] = m_run;
+      s_ml[(warp * AD_MAXG + gid) * 2 + 1] = l_run;
+    }
+  }
+  __syncthreads();
+  float* out = a.partial + ((static_cast<size_t>(b) * a.kv_heads + kvh) * a.splits + split) * G * (HD + 2);
+  for (int i = t; i < G * HD; i += AD_THREADS) {
+    const int g = i / HD, d = i % HD;
+    float M = -INFINITY;
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, s_ml[(w * AD_MAXG + g) * 2]);
+    float acc = 0.f, L = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      const float m = s_ml[(w * AD_MAXG + g) * 2];
+      if (m != -INFINITY) {
+        const float f = __expf(m - M);
+        acc += s_o[(w * AD_MAXG + g) * HD + d] * f;
+        L += s_ml[(w * AD_MAXG + g) * 2 + 1] * f;
+      }
+    }
+    out[g * (HD + 2) + d] = acc;
+    if (d == 0) {
+      out[g * (HD + 2) + HD] = M;
+      out[g * (HD + 2) + HD + 1] = L;
+    }
+  }
+}
+
 // Merges the splits: out[b, head, d] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M).
 __global__ void __launch_bounds__(128)
 attn_decode_merge_kernel(const float* __restrict__ partial, int splits, int G, int hd, int heads, int kv_heads,
@@ -425,6 +678,24 @@ int decode_splits(int bs, int kv_heads, int max_seq_len) {
   if (splits < 1) splits = 1;
   if (splits > 64) splits = 64;
   return splits;
+}
+
+template <typename TC, int HD>
+int launch_decode_mma(const DecodeArgs& a, dim3 grid, cudaStream_t st) {
+  constexpr int RING = ADT_STAGES * 2 * ADT_STAGE_POS * (HD * 2 + 16);
+  constexpr int MERGE = (4 * AD_MAXG * HD + 4 * AD_MAXG * 2) * 4;
+  constexpr int SMEM = RING > MERGE ? RING : MERGE;
+  auto kern = attn_decode_mma_kernel<TC, HD>;
+  static bool configured[16] = {};
+  int dev = 0;
+  B200_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 16 && !configured[dev]) {
+    B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    configured[dev] = true;
+  }
+  kern<<<grid, AD_THREADS, SMEM, st>>>(a);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return B200MOE_OK;
 }
 
 template <typename TC, int HD>
@@ -535,9 +806,10 @@ int b200moe_attn_decode(const void* q, int q_dtype, const void* slab, int cache_
   if (cache_dtype == B200MOE_DT_F32)
     rc = hd == 64 ? launch_decode<float, 64>(a, grid, st) : launch_decode<float, 128>(a, grid, st);
   else if (cache_dtype == B200MOE_DT_F16)
-    rc = hd == 64 ? launch_decode<__half, 64>(a, grid, st) : launch_decode<__half, 128>(a, grid, st);
+    rc = hd == 64 ? launch_decode_mma<__half, 64>(a, grid, st) : launch_decode_mma<__half, 128>(a, grid, st);
   else
-    rc = hd == 64 ? launch_decode<__nv_bfloat16, 64>(a, grid, st) : launch_decode<__nv_bfloat16, 128>(a, grid, st);
+    rc = hd == 64 ? launch_decode_mma<__nv_bfloat16, 64>(a, grid, st)
+                  : launch_decode_mma<__nv_bfloat16, 128>(a, grid, st);
   if (rc) return rc;
   attn_decode_merge_kernel<<<dim3(heads, bs), 128, 0, st>>>(a.partial, a.splits, heads / cache->kv_heads, hd, heads,
                                                             cache->kv_heads, out, out_dtype);
