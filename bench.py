@@ -414,6 +414,8 @@ def main():
                     help="token exchange between ranks: peer-to-peer stores or NCCL all-to-all")
     ap.add_argument("--tokens", type=int, default=0, help="profile_small only: token count")
     ap.add_argument("--kind", default="Q8_0", choices=["Q8_0", "Q4_K"], help="profile_small only")
+    ap.add_argument("--token-tile", type=int, default=0, choices=[0, 64, 128, 192],
+                    help="upper bound of the tensor kernel's token tile (0 = the library's default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
     args = ap.parse_args()
@@ -439,6 +441,8 @@ def main():
     peaks = measured_peaks()
     spec = syn.CASES[spec_name]
     transport = args.ep
+    if args.token_tile:
+        C.check(C.lib.b200moe_set_token_tile(args.token_tile))
 
     # ------------------------------------------ decode attention over the pages
     if args.workload == "attn_decode":

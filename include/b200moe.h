@@ -418,6 +418,13 @@ int b200moe_pipeline_destroy(b200moe_pipeline_t* p);
 int b200moe_profile_enable(int on);
 int b200moe_profile_read(float* ms_out, int32_t* calls_out);
 
+/* Tuning knob (no reference counterpart): upper bound of the single-CTA tensor
+ * kernel's token tile, 64, 128 or 192 rows (0 restores the default, 192).
+ * Narrower tiles leave more tensor memory for staged weights (6 / 4 / 2 slots)
+ * and re-stream the weights once per tile.  Process-wide; results do not depend
+ * on it beyond fp32 summation inside a tile being unchanged (bit-identical). */
+int b200moe_set_token_tile(int32_t rows);
+
 /* Diagnostic (no reference counterpart): while enabled, every launch of the
  * CTA-pair tensor kernel records clock64 time stamps of its first CTA pair's
  * warp roles for the first 256 stages.  b200moe_trace_read synchronises the

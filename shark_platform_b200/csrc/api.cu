@@ -123,6 +123,9 @@ namespace {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Upper bound of the tensor kernels' token tile (b200moe_set_token_tile).
+int g_token_tile = 192;
+
 // Above this many tokens the tensor-memory kernel takes over from the
 // weight-streaming kernel (where the layout allows it).
 constexpr int TENSOR_MIN_TOKENS = 97;
@@ -342,7 +345,7 @@ int b200moe_gate_up(const void* xs, const int32_t* seg_offsets, int32_t pairs,
     return launch_tc_pair_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, out_kperm, a_out,
                                   static_cast<cudaStream_t>(stream));
   if (r == B200MOE_REGIME_TENSOR) {
-    return launch_tc_gate_up(xs, seg_offsets, pairs, 192, gate, up, activation, out_kperm, a_out,
+    return launch_tc_gate_up(xs, seg_offsets, pairs, g_token_tile, gate, up, activation, out_kperm, a_out,
                              static_cast<cudaStream_t>(stream));
   }
   return launch_stream_gate_up(xs, seg_offsets, pairs, max_segment, gate, up, activation,
@@ -371,7 +374,7 @@ int b200moe_down(const void* a, const int32_t* seg_offsets, int32_t pairs, int32
     return launch_tc_pair_down(a, seg_offsets, pairs, 192, down, ksplit, d_out,
                                static_cast<cudaStream_t>(stream));
   if (r == B200MOE_REGIME_TENSOR)
-    return launch_tc_down(a, seg_offsets, pairs, 192, down, ksplit, d_out,
+    return launch_tc_down(a, seg_offsets, pairs, g_token_tile, down, ksplit, d_out,
                           static_cast<cudaStream_t>(stream));
   return launch_stream_down(a, seg_offsets, pairs, max_segment, down, ksplit, d_out,
                             static_cast<cudaStream_t>(stream));
@@ -599,6 +602,12 @@ int b200moe_ep_layer_forward(const b200moe_layer_t* L, const b200moe_ep_t* ep, c
                                 y, io_dtype, st))
       return rc;
   prof_mark(pc, 6, st);
+  return B200MOE_OK;
+}
+
+int b200moe_set_token_tile(int32_t rows) {
+  B200_REQUIRE(rows == 0 || rows == 64 || rows == 128 || rows == 192, "set_token_tile: 0, 64, 128 or 192");
+  g_token_tile = rows == 0 ? 192 : rows;
   return B200MOE_OK;
 }
 
