@@ -26,6 +26,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _cabi as C
+from . import debugging as _debug
 from . import ops as _ops
 
 _DT = {torch.float32: C.DT_F32, torch.float16: C.DT_F16, torch.bfloat16: C.DT_BF16}
@@ -398,7 +399,15 @@ class B200MoeBlock(torch.nn.Module):
             _LAYERS.pop(getattr(self, "_handle", None), None)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return torch.ops.b200moe.layer_forward(h, self._handle, self.regime)
+        if not _debug.flags.any:
+            return torch.ops.b200moe.layer_forward(h, self._handle, self.regime)
+        if _debug.flags.nvtx:
+            torch.cuda.nvtx.range_push(f"b200moe.layer[{h.numel() // h.shape[-1]} tokens]")
+        y, experts, gates = self.layer.forward(h, self.regime, want_routing=True)
+        if _debug.flags.nvtx:
+            torch.cuda.nvtx.range_pop()
+        _debug.after_layer("moe", y, experts, gates)
+        return y
 
 
 class B200MoeStack(torch.nn.Module):

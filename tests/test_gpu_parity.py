@@ -677,3 +677,29 @@ def test_host_pipeline_equals_device_calls(M, depth):
         pipe.submit(torch.zeros(301, case.spec.hidden, dtype=torch.bfloat16), torch.zeros(301, case.spec.hidden, dtype=torch.bfloat16))
     pipe.close()
     assert M.device_status() == 0
+
+
+def test_debug_switches_trace_and_check_a_layer_call(M, tmp_path, capsys):
+    """B200MOE_DEBUG flags: tensor trace, NaN check, per-call dump, NVTX range and
+    a status read around one block call; results unchanged."""
+    from shark_platform_b200 import debugging as dbg
+
+    case = syn.make_case(syn.CASES["small_q8"])
+    blk = b200_block(case)
+    h = device_input(case)
+    want = blk(h)
+    old = dbg.flags
+    dbg.flags = dbg.DebugFlags.parse(f"tensor_trace,nan_checks,nvtx,status_checks,dump_path={tmp_path}")
+    M._debug.flags = dbg.flags
+    try:
+        got = blk(h)
+    finally:
+        dbg.flags = old
+        M._debug.flags = old
+    assert torch.equal(got, want)
+    out = capsys.readouterr().out
+    assert "::: TRACE moe.experts" in out and "::: TRACE moe.output" in out
+    dumped = list(tmp_path.glob("moe_*.pt"))
+    assert len(dumped) == 1
+    d = torch.load(dumped[0])
+    assert d["experts"].shape == (case.spec.tokens, case.spec.top_k)

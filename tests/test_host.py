@@ -200,3 +200,15 @@ def test_patch_moe_blocks_leaves_other_modules_alone():
     model = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.ReLU())
     assert plugin.patch_moe_blocks(model) == 0
     assert isinstance(model[0], torch.nn.Linear)
+
+
+def test_debug_flags_parse_like_the_reference_switch():
+    """B200MOE_DEBUG uses the `[+|-]name[=value]` list syntax of sharktank's
+    TURBINE_LLM_DEBUG (utils/debugging.py:28-83)."""
+    from shark_platform_b200 import debugging as dbg
+
+    f = dbg.DebugFlags.parse("tensor_trace, +nvtx,-nan_checks,dump_path=/tmp/b200moe_dump")
+    assert f.tensor_trace and f.nvtx and not f.nan_checks and str(f.dump_path) == "/tmp/b200moe_dump" and f.any
+    assert not dbg.DebugFlags.parse("").any
+    with pytest.raises(ValueError):
+        dbg.DebugFlags.parse("no_such_flag")
