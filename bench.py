@@ -416,6 +416,8 @@ def main():
     ap.add_argument("--kind", default="Q8_0", choices=["Q8_0", "Q4_K"], help="profile_small only")
     ap.add_argument("--token-tile", type=int, default=0, choices=[0, 64, 128, 192],
                     help="upper bound of the tensor kernel's token tile (0 = the library's default)")
+    ap.add_argument("--stream-wide", type=int, default=-1, choices=[-1, 0, 1],
+                    help="streaming kernel: 16 consumer warps (1), 8 (0), by layout (-1, the default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
     args = ap.parse_args()
@@ -443,6 +445,8 @@ def main():
     transport = args.ep
     if args.token_tile:
         C.check(C.lib.b200moe_set_token_tile(args.token_tile))
+    if args.stream_wide >= 0:
+        C.check(C.lib.b200moe_set_stream_wide(args.stream_wide))
 
     # ------------------------------------------ decode attention over the pages
     if args.workload == "attn_decode":

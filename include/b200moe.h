@@ -425,6 +425,14 @@ int b200moe_profile_read(float* ms_out, int32_t* calls_out);
  * on it beyond fp32 summation inside a tile being unchanged (bit-identical). */
 int b200moe_set_token_tile(int32_t rows);
 
+/* Tuning knob (no reference counterpart): warp geometry of the streaming kernel
+ * for chunks of up to 32 tokens.  1 = sixteen consumer warps per CTA (each stage's
+ * reduction range split four ways), 0 = eight, -1 (default) = sixteen for the
+ * quantised layouts, eight for dense fp16 weights.
+ * Process-wide.  The fp32 summation order inside a stage differs between the two
+ * geometries, so results agree to rounding, not bit for bit. */
+int b200moe_set_stream_wide(int32_t mode);
+
 /* Diagnostic (no reference counterpart): while enabled, every launch of the
  * CTA-pair tensor kernel records clock64 time stamps of its first CTA pair's
  * warp roles for the first 256 stages.  b200moe_trace_read synchronises the

@@ -142,6 +142,7 @@ _PROTOS = {
     "b200moe_pipeline_drain": (c_int, [_P]),
     "b200moe_pipeline_destroy": (c_int, [_P]),
     "b200moe_set_token_tile": (c_int, [c_int32]),
+    "b200moe_set_stream_wide": (c_int, [c_int32]),
     "b200moe_trace_enable": (c_int, [c_int]),
     "b200moe_trace_read": (c_int, [POINTER(c_int64), c_size_t]),
     "b200moe_profile_enable": (c_int, [c_int]),

@@ -611,6 +611,12 @@ int b200moe_set_token_tile(int32_t rows) {
   return B200MOE_OK;
 }
 
+int b200moe_set_stream_wide(int32_t mode) {
+  B200_REQUIRE(mode >= -1 && mode <= 1, "set_stream_wide: -1 (by layout), 0 or 1");
+  set_stream_wide(mode);
+  return B200MOE_OK;
+}
+
 int b200moe_trace_enable(int on) { return pair_trace_enable(on != 0); }
 
 int b200moe_trace_read(int64_t* out, size_t count) {

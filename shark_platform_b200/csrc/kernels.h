@@ -41,6 +41,8 @@ int launch_stream_gate_up(const void* xs, const int32_t* seg, int pairs, int max
                           int out_kperm, void* a_out, cudaStream_t st);
 int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_segment,
                        const b200moe_weight_t* down, int ksplit, float* d_out, cudaStream_t st);
+// -1 = wide geometry (16 consumer warps) by layout, 0 = never, 1 = always
+void set_stream_wide(int mode);
 
 // prefill regime (tc_gemm.cu)
 bool tc_supported(const b200moe_weight_t* w, bool down);

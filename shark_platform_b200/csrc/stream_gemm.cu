@@ -22,8 +22,6 @@ namespace b200moe {
 
 namespace {
 
-constexpr int CONSUMER_WARPS = 8;
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int KT = 256;   // reduction elements per stage
 constexpr int MAX_E = 64;
 
@@ -54,15 +52,20 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
       : "memory");
 }
 
-// RW = row warps per k half: 4 (64 rows per set, two k halves, 8 consumer warps)
-// or 7 (112 rows per set, one k pass, 7 consumer warps): 112-row tiles divide
-// ffn sizes with a factor 7 (14336 = 128 x 112) into a number of work items
-// that fills the last wave of SMs.
-template <int LAYOUT, int S, int RW>
+// RW = row warps per k part: 4 (64 rows per set) or 7 (112 rows per set: 112-row
+// tiles divide ffn sizes with a factor 7 (14336 = 128 x 112) into a number of
+// work items that fills the last wave of SMs).  KH = k parts of a stage handled
+// by different warps (the parts are added through shared memory at the end of an
+// item).  Consumer warps = RW * KH: (4,2) = 8 and (7,1) = 7 are the narrow
+// geometries, (4,4) = 16 and (7,2) = 14 the wide ones — the same tiles with twice
+// the warps, for layouts whose dequantisation is instruction-bound.
+template <int LAYOUT, int S, int RW, int KH_>
 struct Cfg {
   static constexpr int SET_ROWS = 16 * RW;
-  static constexpr int KH = RW == 4 ? 2 : 1;   // k halves handled by different warps
-  static constexpr int ACTIVE = RW * KH;       // consumer warps that work
+  static constexpr int KH = KH_;               // k parts handled by different warps
+  static constexpr int ACTIVE = RW * KH;       // consumer warps
+  static constexpr int GROUP = RW * 32;        // threads of one k part
+  static constexpr int THREADS = (ACTIVE + 1) * 32;  // + the TMA producer warp
   static constexpr int MT = 8 * S;  // tokens per chunk
   // bytes of one row set of quantised values per stage
   static constexpr int WSET = LAYOUT == B200MOE_LAYOUT_Q8_0   ? SET_ROWS * KT
@@ -75,8 +78,9 @@ struct Cfg {
   static constexpr int OFF_X = 2 * WSET;
   static constexpr int OFF_S = OFF_X + 4 * XBOX;
   static constexpr int STAGE = (OFF_S + 2 * SSET + 1023) / 1024 * 1024;
-  static constexpr int RED_FLOATS = 8 * S < 32 ? 8 * S : 32;  // floats per thread per reduce round
-  static constexpr int RED_BYTES = 128 * RED_FLOATS * 4;
+  // floats per thread per reduce round (fewer with more source parts: each part has a buffer)
+  static constexpr int RED_FLOATS = KH > 2 ? 8 : (8 * S < 32 ? 8 * S : 32);
+  static constexpr int RED_BYTES = (KH > 1 ? KH - 1 : 1) * GROUP * RED_FLOATS * 4;  // one buffer per source part
   static constexpr int BUDGET = 232448 - 1024 - RED_BYTES - 256;
   static constexpr int STAGES_RAW = BUDGET / STAGE;
   static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
@@ -92,17 +96,18 @@ __device__ __forceinline__ __half2 bcast_half(uint32_t v, int sel) {
   return u32_as_h2(__byte_perm(v, v, sel ? 0x3232 : 0x1010));
 }
 
-template <int LAYOUT, int NMAT, int S, int RW>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int LAYOUT, int NMAT, int S, int RW, int KH_>
+__global__ void __launch_bounds__((RW * KH_ + 1) * 32, 1)
 stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                    const __grid_constant__ CUtensorMap tm_s0, const __grid_constant__ CUtensorMap tm_s1,
                    const __grid_constant__ CUtensorMap tm_x8, const __grid_constant__ CUtensorMap tm_x16,
                    const __grid_constant__ CUtensorMap tm_x32, const __grid_constant__ CUtensorMap tm_x64,
                    const StreamArgs args) {
-  using C = Cfg<LAYOUT, S, RW>;
+  using C = Cfg<LAYOUT, S, RW, KH_>;
   constexpr int STAGES = C::STAGES;
   constexpr int SET_ROWS = C::SET_ROWS;
   constexpr int KH = C::KH;
+  constexpr int GROUP = C::GROUP;
   constexpr int SPANS = 4 / KH;  // 64-k spans of a stage per warp
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_seg[MAX_E + 1];
@@ -154,7 +159,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
     rows = min(C::MT, s_seg[e + 1] - row0);
   };
 
-  if (warp == CONSUMER_WARPS) {
+  if (warp == C::ACTIVE) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       uint32_t n = 0;
@@ -216,11 +221,10 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
   }
 
   // -------------------------------------------------------------- consumers
-  if (warp >= C::ACTIVE) return;  // RW = 7 leaves one consumer warp without rows
   const int w = warp % RW, kh = warp / RW;
   const int g = lane >> 2, t = lane & 3;
   const int rg = rho(g);
-  const int ctid = tid & 127;  // index within a k-half group
+  const int ctid = tid % GROUP;  // index within a k-part group
   uint32_t n = 0;
 
   for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
@@ -242,12 +246,16 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
       const uint32_t sb = smem_base + slot * C::STAGE;
 
       if constexpr (LAYOUT == B200MOE_LAYOUT_Q8_0) {
-        uint32_t sc[2][2][4];  // [set][row half][8 block scales of the stage]
+        uint32_t sc[2][2][SPANS];  // [set][row half][the two block scales of each of the warp's spans]
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          const uint32_t srow = sb + C::OFF_S + r * C::SSET + (16 * w + rg) * 16;
-          lds128(srow, sc[r][0]);
-          lds128(srow + 8 * 16, sc[r][1]);
+          const uint32_t srow = sb + C::OFF_S + r * C::SSET + (16 * w + rg) * 16 + kh * SPANS * 4;
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            if constexpr (SPANS == 4) lds128(srow + hf * 8 * 16, sc[r][hf]);
+            else if constexpr (SPANS == 2) lds64(srow + hf * 8 * 16, sc[r][hf]);
+            else sc[r][hf][0] = lds32(srow + hf * 8 * 16);
+          }
         }
 #pragma unroll
         for (int spi = 0; spi < SPANS; ++spi) {
@@ -262,7 +270,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
             for (int hf = 0; hf < 2; ++hf) {
               uint32_t q[4];
               lds128(wbase + hf * 8 * 128, q);
-              const uint32_t sw = (KH == 2 && kh) ? sc[r][hf][(2 + spi) & 3] : sc[r][hf][spi];
+              const uint32_t sw = sc[r][hf][spi];
               const __half2 scale = bcast_half(sw, t >> 1);
 #pragma unroll
               for (int j = 0; j < 4; ++j) dequant_q8x4(q[j], scale, alo[r][hf][j], ahi[r][hf][j]);
@@ -371,27 +379,33 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
       if (lane == 0) mbar_arrive(empty_bar(slot));
     }
 
-    if constexpr (KH == 2) {
-      // ---- add the two k halves: kh=1 warps hand their sums to kh=0 warps
+    if constexpr (KH > 1) {
+      // ---- add the k parts: parts 1.. hand their sums to part 0, each through
+      // its own buffer
       constexpr int TOTAL = 8 * S;
       constexpr int ROUNDS = TOTAL / C::RED_FLOATS;
+      constexpr int BUF = GROUP * C::RED_FLOATS;  // floats of one part's buffer
       float* accf = &acc[0][0][0];
       float* red = reinterpret_cast<float*>(smem_raw + (red_base - smem_u32(smem_raw)));
 #pragma unroll
       for (int rd = 0; rd < ROUNDS; ++rd) {
-        if (kh == 1) {
+        if (kh > 0) {
 #pragma unroll
-          for (int i = 0; i < C::RED_FLOATS; ++i) red[i * 128 + ctid] = accf[rd * C::RED_FLOATS + i];
+          for (int i = 0; i < C::RED_FLOATS; ++i)
+            red[(kh - 1) * BUF + i * GROUP + ctid] = accf[rd * C::RED_FLOATS + i];
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(KH * GROUP) : "memory");
         if (kh == 0) {
 #pragma unroll
-          for (int i = 0; i < C::RED_FLOATS; ++i) accf[rd * C::RED_FLOATS + i] += red[i * 128 + ctid];
+          for (int src = 0; src < KH - 1; ++src)
+#pragma unroll
+            for (int i = 0; i < C::RED_FLOATS; ++i)
+              accf[rd * C::RED_FLOATS + i] += red[src * BUF + i * GROUP + ctid];
           // one thread decides for all consumers whether the CTA gives up, so
           // that every warp leaves the item loop at the same barrier
           if (rd == ROUNDS - 1 && ctid == 0) s_exit = *abort_flag;
         }
-        asm volatile("bar.sync 2, 256;" ::: "memory");
+        asm volatile("bar.sync 2, %0;" ::"n"(KH * GROUP) : "memory");
       }
       if (s_exit) break;
       if (kh != 0) continue;
@@ -428,10 +442,10 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_const
   }
 }
 
-template <int LAYOUT, int NMAT, int S, int RW>
+template <int LAYOUT, int NMAT, int S, int RW, int KH>
 int launch_t(const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
-  using C = Cfg<LAYOUT, S, RW>;
-  auto kern = stream_gemm_kernel<LAYOUT, NMAT, S, RW>;
+  using C = Cfg<LAYOUT, S, RW, KH>;
+  auto kern = stream_gemm_kernel<LAYOUT, NMAT, S, RW, KH>;
   static bool configured[16] = {};
   int dev = 0;
   B200_CHECK_CUDA(cudaGetDevice(&dev));
@@ -439,20 +453,43 @@ int launch_t(const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
     B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     configured[dev] = true;
   }
-  kern<<<sm_count(), THREADS, C::SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+  kern<<<sm_count(), C::THREADS, C::SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
                                              maps[6], maps[7], a);
   B200_CHECK_CUDA(cudaGetLastError());
   return B200MOE_OK;
 }
 
-template <int LAYOUT, int NMAT, int RW>
+template <int LAYOUT, int NMAT, int RW, int KH>
 int launch_s(int S, const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
   switch (S) {
-    case 1: return launch_t<LAYOUT, NMAT, 1, RW>(maps, a, st);
-    case 2: return launch_t<LAYOUT, NMAT, 2, RW>(maps, a, st);
-    case 4: return launch_t<LAYOUT, NMAT, 4, RW>(maps, a, st);
-    default: return launch_t<LAYOUT, NMAT, 8, RW>(maps, a, st);
+    case 1: return launch_t<LAYOUT, NMAT, 1, RW, KH>(maps, a, st);
+    case 2: return launch_t<LAYOUT, NMAT, 2, RW, KH>(maps, a, st);
+    case 4: return launch_t<LAYOUT, NMAT, 4, RW, KH>(maps, a, st);
+    default: return launch_t<LAYOUT, NMAT, 8, RW, KH>(maps, a, st);
   }
+}
+
+// 64-row sets with four k parts (16 consumer warps), chunks of up to 32 tokens
+template <int LAYOUT, int NMAT>
+int launch_w(int S, const CUtensorMap* maps, const StreamArgs& a, cudaStream_t st) {
+  switch (S) {
+    case 1: return launch_t<LAYOUT, NMAT, 1, 4, 4>(maps, a, st);
+    case 2: return launch_t<LAYOUT, NMAT, 2, 4, 4>(maps, a, st);
+    default: return launch_t<LAYOUT, NMAT, 4, 4, 4>(maps, a, st);
+  }
+}
+
+// Twice the consumer warps on the same tiles (b200moe_set_stream_wide): -1 = for
+// every quantised layout (measured at 32 tokens: Q4_K 0.354 -> 0.322 ms, Q8_0
+// 0.317 -> 0.306 ms per layer; the kernel is bound by instruction issue, not by
+// bytes, below that), 0 = never, 1 = always.  Chunks of more than 32 tokens keep
+// the narrow geometry (registers); dense fp16 weights have no wide instance.
+int g_stream_wide = -1;
+
+bool use_wide(int layout, int S) {
+  if (S > 4) return false;
+  if (g_stream_wide >= 0) return g_stream_wide != 0;
+  return layout == B200MOE_LAYOUT_Q4_K || layout == B200MOE_LAYOUT_Q8_0;
 }
 
 int weight_maps(const b200moe_weight_t* w, CUtensorMap* tw, CUtensorMap* ts, int SET_ROWS = 64) {
@@ -567,13 +604,20 @@ int launch_stream_gate_up(const void* xs, const int32_t* seg, int pairs, int max
   }
   a.total_rows = static_cast<long long>(gate->experts) * gate->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
+  const bool wide = use_wide(gate->layout, S);
   if (set_rows == 112) {
-    return S == 1 ? launch_t<B200MOE_LAYOUT_Q8_0, 2, 1, 7>(maps, a, st)
-                  : launch_t<B200MOE_LAYOUT_Q8_0, 2, 2, 7>(maps, a, st);
+    if (wide)
+      return S == 1 ? launch_t<B200MOE_LAYOUT_Q8_0, 2, 1, 7, 2>(maps, a, st)
+                    : launch_t<B200MOE_LAYOUT_Q8_0, 2, 2, 7, 2>(maps, a, st);
+    return S == 1 ? launch_t<B200MOE_LAYOUT_Q8_0, 2, 1, 7, 1>(maps, a, st)
+                  : launch_t<B200MOE_LAYOUT_Q8_0, 2, 2, 7, 1>(maps, a, st);
   }
-  if (gate->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 2, 4>(S, maps, a, st);
-  if (gate->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 2, 4>(S, maps, a, st);
-  return launch_s<B200MOE_LAYOUT_Q4_K, 2, 4>(S, maps, a, st);
+  if (gate->layout == B200MOE_LAYOUT_Q8_0)
+    return wide ? launch_w<B200MOE_LAYOUT_Q8_0, 2>(S, maps, a, st)
+                : launch_s<B200MOE_LAYOUT_Q8_0, 2, 4, 2>(S, maps, a, st);
+  if (gate->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 2, 4, 2>(S, maps, a, st);
+  return wide ? launch_w<B200MOE_LAYOUT_Q4_K, 2>(S, maps, a, st)
+              : launch_s<B200MOE_LAYOUT_Q4_K, 2, 4, 2>(S, maps, a, st);
 }
 
 int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_segment,
@@ -599,9 +643,15 @@ int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_
     a.st0 = a.st1 = static_cast<const uint8_t*>(down->sub);
   a.total_rows = static_cast<long long>(down->experts) * down->rows;
   if (a.status == nullptr) return B200MOE_ERR_CUDA;
-  if (down->layout == B200MOE_LAYOUT_Q8_0) return launch_s<B200MOE_LAYOUT_Q8_0, 1, 4>(S, maps, a, st);
-  if (down->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 1, 4>(S, maps, a, st);
-  return launch_s<B200MOE_LAYOUT_Q4_K, 1, 4>(S, maps, a, st);
+  const bool wide = use_wide(down->layout, S);
+  if (down->layout == B200MOE_LAYOUT_Q8_0)
+    return wide ? launch_w<B200MOE_LAYOUT_Q8_0, 1>(S, maps, a, st)
+                : launch_s<B200MOE_LAYOUT_Q8_0, 1, 4, 2>(S, maps, a, st);
+  if (down->layout == B200MOE_LAYOUT_F16) return launch_s<B200MOE_LAYOUT_F16, 1, 4, 2>(S, maps, a, st);
+  return wide ? launch_w<B200MOE_LAYOUT_Q4_K, 1>(S, maps, a, st)
+              : launch_s<B200MOE_LAYOUT_Q4_K, 1, 4, 2>(S, maps, a, st);
 }
+
+void set_stream_wide(int mode) { g_stream_wide = mode; }
 
 }  // namespace b200moe

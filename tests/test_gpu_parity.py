@@ -496,6 +496,30 @@ def test_stream_kernel_112_row_tiles(M, tokens, skew):
     assert orc.rel_l2(y.cpu() - case.h, want - case.h) < REL_L2_TOL
 
 
+@pytest.mark.parametrize("wide", [0, 1])
+@pytest.mark.parametrize("kind,ffn", [(syn.Q8_0, 512), (syn.Q4_K, 512), (syn.Q8_0, 14336)])
+@pytest.mark.parametrize("tokens", [1, 9, 32, 33])
+def test_stream_kernel_warp_geometries(M, wide, kind, ffn, tokens):
+    """The streaming kernel with eight and with sixteen consumer warps (the k range
+    of a stage split two or four ways; 7 or 14 warps on 112-row tiles) against the
+    oracle; 33 tokens reach chunks that keep the narrow geometry either way."""
+    from shark_platform_b200 import _cabi as C
+
+    spec = syn.CaseSpec("geom", tokens, 256, ffn, kind=kind, seed=900 + tokens, act_dtype="f32")
+    case = syn.make_case(spec)
+    want, mid = orc.moe_block(case.h, oracle_params(case), form="per_expert")
+    blk = b200_block(case, regime="stream")
+    C.check(C.lib.b200moe_set_stream_wide(wide))
+    try:
+        y, experts, _ = blk.layer.forward(case.h.cuda(), regime=M.REGIMES["stream"], want_routing=True)
+        torch.cuda.synchronize()
+    finally:
+        C.check(C.lib.b200moe_set_stream_wide(-1))
+    assert M.device_status() == 0
+    assert torch.equal(experts.cpu().to(torch.int64), mid["experts"])
+    assert orc.rel_l2(y.cpu() - case.h, want - case.h) < REL_L2_TOL
+
+
 @pytest.mark.parametrize("ksplit", [2, 4])
 def test_tensor_down_ksplit_partials_sum_to_the_unsplit_result(M, ksplit):
     from shark_platform_b200 import _cabi as C, types as T
