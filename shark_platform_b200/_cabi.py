@@ -11,7 +11,8 @@ import re
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "lib", "libb200moe.so")
+# B200MOE_LIB points at another build of the same library (e.g. a diagnostic build)
+LIB_PATH = os.environ.get("B200MOE_LIB") or os.path.join(HERE, "lib", "libb200moe.so")
 HEADER_PATH = os.path.join(os.path.dirname(HERE), "include", "b200moe.h")
 
 LAYOUT_Q8_0, LAYOUT_Q4_K, LAYOUT_F16 = 0, 1, 2

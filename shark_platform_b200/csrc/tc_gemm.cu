@@ -171,6 +171,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -408,6 +416,93 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     const int sw = row & 7;                 // 128-byte swizzle term of this row
     uint32_t n = 0, ti = 0;
     bool ok = true;
+
+    // Drains the two accumulators of a finished tile.  Each of the four
+    // (group, set) warp sets takes every fourth 16-token column chunk.
+    auto epilogue = [&](int nt, int row0, int rows, int ncols, uint32_t tix) -> bool {
+      if (!mbar_wait_warp(acc_full_bar, tix & 1u, abort_flag, args.status)) return false;
+      tc_fence_after();
+      if constexpr (NMAT == 2) {
+        int col = (nt & 0xffff) * TC_ROWS + row;
+        if (args.out_kperm) col = (col & ~7) | ((col & 3) << 1) | ((col >> 2) & 1);
+        __half* obase = static_cast<__half*>(args.out) + static_cast<size_t>(row0) * args.N + col;
+        const size_t ostride = static_cast<size_t>(args.N);
+        const bool silu = args.act == B200MOE_ACT_SILU;
+        float amax = 0.f;
+        for (int c0 = (grp * 2 + set) * 16; c0 < ncols; c0 += 64) {
+#pragma unroll 1
+          for (int h8 = 0; h8 < 16; h8 += 8) {
+            uint32_t g[8], u[8];
+            tmem_ld8(tmem + lane_addr + TC_COL_ACC0 + c0 + h8, g);
+            tmem_ld8(tmem + lane_addr + TC_COL_ACC1 + c0 + h8, u);
+            tmem_wait_ld();
+            __half* o = obase + static_cast<size_t>(c0 + h8) * ostride;
+            const int lim = rows - c0 - h8;  // token rows of the segment among these eight
+            if (lim >= 8) {
+              if (silu) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float v = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+                  amax = fmaxf(amax, fabsf(v));
+                  o[j * ostride] = to_half_sat(v);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float v = gelu_erf_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+                  amax = fmaxf(amax, fabsf(v));
+                  o[j * ostride] = to_half_sat(v);
+                }
+              }
+            } else {
+              // columns past the segment are products with another expert's
+              // token rows: neither stored nor range-checked
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (j < lim) {
+                  const float gv = __uint_as_float(g[j]);
+                  const float v = (silu ? silu_f(gv) : gelu_erf_f(gv)) * __uint_as_float(u[j]);
+                  amax = fmaxf(amax, fabsf(v));
+                  o[j * ostride] = to_half_sat(v);
+                }
+              }
+            }
+          }
+        }
+        if (amax >= 65520.0f) atomicOr(args.status, DEV_WARN_SATURATED);
+      } else {
+        float* obase = static_cast<float*>(args.out) + static_cast<size_t>(nt >> 16) * args.P * args.N +
+                       static_cast<size_t>(row0) * args.N + (nt & 0xffff) * (2 * TC_ROWS) + row;
+        const size_t ostride = static_cast<size_t>(args.N);
+        for (int c0 = (grp * 2 + set) * 16; c0 < ncols; c0 += 64) {
+          uint32_t g[16], u[16];
+          tmem_ld16(tmem + lane_addr + TC_COL_ACC0 + c0, g);
+          tmem_ld16(tmem + lane_addr + TC_COL_ACC1 + c0, u);
+          tmem_wait_ld();
+          float* o = obase + static_cast<size_t>(c0) * ostride;
+          const int lim = rows - c0;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (j < lim) {
+              o[j * ostride] = __uint_as_float(g[j]);
+              o[j * ostride + TC_ROWS] = __uint_as_float(u[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar);
+      return true;
+    };
+
+    // The epilogue of tile t runs after this warp has handed the first stage of
+    // tile t+1 to its issuer (the A ring gives each group one slot, so exactly
+    // one stage can be staged ahead): the wait for tile t's last MMAs and the
+    // restart of the pipeline overlap.
+    bool have_prev = false;
+    int p_nt = 0, p_row0 = 0, p_rows = 0, p_ncols = 0;
+    uint32_t p_ti = 0;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
       int e, nt, row0, rows, ncols;
       decode(tile, e, nt, row0, rows, ncols);
@@ -479,42 +574,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
           // serialise in shared memory
           __syncwarp();
           if (lane == 0) mbar_arrive(a_ready + 8u * (2 * as + set));
-        }
-      }
-      if (!ok) break;
-      // ---- epilogue: each of the four warpgroups takes every fourth 16-token column chunk
-      if (!mbar_wait_warp(acc_full_bar, ti & 1u, abort_flag, args.status)) break;
-      tc_fence_after();
-      const int seg_end = row0 + rows;
-      for (int c0 = (grp * 2 + set) * 16; c0 < ncols; c0 += 64) {
-        uint32_t g[16], u[16];
-        tmem_ld16(tmem + lane_addr + TC_COL_ACC0 + c0, g);
-        tmem_ld16(tmem + lane_addr + TC_COL_ACC1 + c0, u);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int tok = row0 + c0 + j;
-          if (tok >= seg_end) continue;
-          if constexpr (NMAT == 2) {
-            const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
-            const float a = args.act == B200MOE_ACT_SILU ? silu_f(gv) : gelu_erf_f(gv);
-            int col = (nt & 0xffff) * TC_ROWS + row;
-            if (args.out_kperm) col = (col & ~7) | ((col & 3) << 1) | ((col >> 2) & 1);
-            static_cast<__half*>(args.out)[static_cast<size_t>(tok) * args.N + col] = to_half_sat(a * uv, args.status);
-          } else {
-            float* o = static_cast<float*>(args.out) +
-                       static_cast<size_t>(nt >> 16) * args.P * args.N +
-                       static_cast<size_t>(tok) * args.N + (nt & 0xffff) * (2 * TC_ROWS) + row;
-            o[0] = __uint_as_float(g[j]);
-            o[TC_ROWS] = __uint_as_float(u[j]);
+          if (s4 < 2 && sg == 0 && have_prev) {
+            have_prev = false;
+            if (!epilogue(p_nt, p_row0, p_rows, p_ncols, p_ti)) { ok = false; break; }
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty_bar);
+      if (!ok) break;
+      have_prev = true;
+      p_nt = nt; p_row0 = row0; p_rows = rows; p_ncols = ncols; p_ti = ti;
     }
+    if (ok && have_prev) epilogue(p_nt, p_row0, p_rows, p_ncols, p_ti);
   }
+
 
   // ---- teardown: everyone is done with tensor memory before it is freed
   tc_fence_before();
