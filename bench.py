@@ -823,18 +823,59 @@ def main():
             yp.copy_(block(h_dev), non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
+        def timed(fn):
+            barrier()
+            t0 = time.perf_counter()
+            fn()
+            barrier()
+            dt = torch.tensor([time.perf_counter() - t0], device=dev)
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            return tokens * args.steps / float(dt.item())
+
         for _ in range(3):
             e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_step()
-        barrier()
-        dt = torch.tensor([time.perf_counter() - t0], device=dev)
-        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-        e2e = {"value": tokens * args.steps / float(dt.item()), "unit": "tokens/s",
+        one_at_a_time = timed(lambda: [e2e_step() for _ in range(args.steps)])
+
+        # Two steps in flight: the copy-in of step i+1 and the copy-out of step
+        # i-1 run on their own streams beside the layer call of step i; the host
+        # reads every step's result (waits for its copy-out) one step later.
+        depth = 2
+        comp = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        h_devs = [torch.empty_like(h) for _ in range(depth)]
+        yps = [torch.empty_like(hp).pin_memory() for _ in range(depth)]
+        ev_in = [torch.cuda.Event() for _ in range(depth)]
+        ev_comp = [torch.cuda.Event() for _ in range(depth)]
+        ev_out = [torch.cuda.Event() for _ in range(depth)]
+
+        def pipelined(steps):
+            for i in range(steps):
+                s = i % depth
+                with torch.cuda.stream(s_in):
+                    if i >= depth:
+                        s_in.wait_event(ev_comp[s])  # the layer of step i-depth has read this buffer
+                    h_devs[s].copy_(hp, non_blocking=True)
+                    ev_in[s].record(s_in)
+                comp.wait_event(ev_in[s])
+                y = block(h_devs[s])
+                ev_comp[s].record(comp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_comp[s])
+                    yps[s].copy_(y, non_blocking=True)
+                    y.record_stream(s_out)
+                    ev_out[s].record(s_out)
+                if i >= 1:
+                    ev_out[(i - 1) % depth].synchronize()
+            ev_out[(steps - 1) % depth].synchronize()
+
+        pipelined(3)
+        torch.cuda.synchronize()
+        piped = timed(lambda: pipelined(args.steps))
+        torch.cuda.synchronize()
+        e2e = {"value": piped, "unit": "tokens/s",
                "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": nbytes * world,
-               "steps_in_flight": 1}
+               "steps_in_flight": depth, "one_step_at_a_time": one_at_a_time,
+               "pipelined_equals_serial": bool(torch.equal(yps[(args.steps - 1) % depth], yp))}
         l2_cold = None
 
     if rank == 0:
