@@ -326,8 +326,14 @@ def e2e_pipeline(C, moe, layer, h, steps, regime, depth):
     yp = [torch.empty_like(hp[0]).pin_memory() for _ in range(max(depth, 1))]
     nbytes = hp[0].numel() * hp[0].element_size()
     pipe = moe.HostPipeline(layer, tokens, h.dtype, depth=depth, regime=regime)
-    for i in range(3):
-        pipe.submit(hp[i % depth], yp[i % depth])
+    # the same soak as the device-timed region: the pipeline runs for SOAK_S
+    # seconds first, so that the timed steps see the settled clock and not the
+    # boost the GPU returns to while the host sets the pipeline up
+    soaked = 0
+    t_end = time.perf_counter() + SOAK_S
+    while time.perf_counter() < t_end or soaked < 3:
+        pipe.submit(hp[soaked % depth], yp[soaked % depth])  # waits for its slot: at most `depth` in flight
+        soaked += 1
     pipe.drain()
     t0 = time.perf_counter()
     for i in range(steps):
@@ -337,7 +343,8 @@ def e2e_pipeline(C, moe, layer, h, steps, regime, depth):
     y_last = yp[(steps - 1) % depth].to(dev)
     pipe.close()
     return {"value": tokens * steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": nbytes,
-            "d2h_bytes_per_step": nbytes, "steps_in_flight": depth}, y_last
+            "d2h_bytes_per_step": nbytes, "steps_in_flight": depth,
+            "soak_steps_before_timing": soaked}, y_last
 
 
 def measure_layer(C, moe, syn, block, h, spec, args, peaks, sampler=None, cold=True):
