@@ -75,8 +75,12 @@ struct TcCfg {
   static_assert(NMAX == 64 || NMAX == 128 || NMAX == 192, "token tile widths: 64, 128, 192");
   static constexpr int ASLOTS = (512 - 2 * NMAX) / 64;  // 6, 4, 2 (even: a slot belongs to one dequant group)
   static constexpr int WSLOTS = NMAX == 192 ? 2 : NMAX == 128 ? 3 : 5;
-  static constexpr int XSLOTS = 6;
-  static constexpr int XSLOT = NMAX * TC_KT * 2;
+  // a token slot holds two 64-k stages (two swizzled sub-tiles of NMAX rows x 128 B):
+  // one wait and one release per 128 k on the issuing lanes, whose instruction
+  // stream is the kernel's critical path
+  static constexpr int XSLOTS = 3;
+  static constexpr int XSUB = NMAX * TC_KT * 2;
+  static constexpr int XSLOT = 2 * XSUB;
   static constexpr int OFF_X = WSLOTS * TC_WSLOT;
   static constexpr int OFF_S = OFF_X + XSLOTS * XSLOT;
   static constexpr int OFF_BAR = OFF_S + TC_SSLOTS * TC_SSLOT;
@@ -144,6 +148,26 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The four K=16 MMAs of a 64-k stage in one statement: A at a_tmem + 8 j columns,
+// B descriptors differing in the start-address field only (32 bytes = 2 units
+// per K step; the upper descriptor word is constant).  The first one overwrites
+// the accumulator when `accumulate` is 0.
+__device__ __forceinline__ void tc_mma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo,
+                                             uint32_t b_desc_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 d0, d1, d2, d3;\n\t.reg .b32 l1, l2, l3, a1, a2, a3;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.ne.b32 t, %4, 0;\n\t"
+      "add.u32 l1, %2, 2;\n\tadd.u32 l2, %2, 4;\n\tadd.u32 l3, %2, 6;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
+      "mov.b64 d0, {%2, %3};\n\tmov.b64 d1, {l1, %3};\n\tmov.b64 d2, {l2, %3};\n\tmov.b64 d3, {l3, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d0, %4, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], d1, %4, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], d2, %4, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], d3, %4, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -214,7 +238,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
   __shared__ uint32_t s_tmem;
 
   using G = TcCfg<NMAX>;
-  constexpr int TC_WSLOTS = G::WSLOTS, TC_XSLOTS = G::XSLOTS, TC_XSLOT = G::XSLOT, TC_ASLOTS = G::ASLOTS;
+  constexpr int TC_WSLOTS = G::WSLOTS, TC_XSLOTS = G::XSLOTS, TC_XSLOT = G::XSLOT, TC_XSUB = G::XSUB, TC_ASLOTS = G::ASLOTS;
   constexpr uint32_t TC_COL_ACC0 = G::COL_ACC0, TC_COL_ACC1 = G::COL_ACC1, TC_COL_A = G::COL_A;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t x_base = smem_base + G::OFF_X;
@@ -359,12 +383,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
                               : ncols <= 96 ? &tm_x96 : ncols <= 128 ? &tm_x128 : &tm_x192;
         const uint32_t xbytes = (ncols <= 16 ? 16 : ncols <= 32 ? 32 : ncols <= 64 ? 64
                                : ncols <= 96 ? 96 : ncols <= 128 ? 128 : 192) * 128;
-        for (int st = 0; st < stages_per_tile; ++st, ++n) {
+        for (int st = 0; st < stages_per_tile; st += 2, ++n) {  // n counts slots = pairs of stages
           const int xs = n % TC_XSLOTS;
           if (!mbar_wait(xempty + 8u * xs, ((n / TC_XSLOTS) & 1u) ^ 1u, abort_flag, args.status)) { ok = false; break; }
           const uint32_t xb = xfull + 8u * xs;
-          mbar_expect_tx(xb, xbytes);
-          tma_load_2d(x_base + xs * TC_XSLOT, tx, ((nt >> 16) * stages_per_tile + st) * TC_KT * 2, row0, xb);
+          const int x0 = ((nt >> 16) * stages_per_tile + st) * TC_KT * 2;
+          mbar_expect_tx(xb, 2 * xbytes);
+          tma_load_2d(x_base + xs * TC_XSLOT, tx, x0, row0, xb);
+          tma_load_2d(x_base + xs * TC_XSLOT + TC_XSUB, tx, x0 + TC_KT * 2, row0, xb);
         }
       }
       for (uint32_t i = n > (uint32_t)TC_XSLOTS ? n - TC_XSLOTS : 0; i < n; ++i)
@@ -375,33 +401,38 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant_
     if (lane == 0) {
       const int mset = warp - TC_WARP_MMA;
       const uint32_t acc = tmem + (mset == 0 ? TC_COL_ACC0 : TC_COL_ACC1);
-      uint32_t n = 0, ti = 0;
+      uint32_t ti = 0;
       bool ok = true;
+      // slot indices and phase parities advance by counters: this lane's
+      // instruction stream is the kernel's critical path (every instruction of
+      // it was measured at 15-20 clocks beside the sixteen dequantising warps)
+      uint32_t xs = 0, xph = 0, as = 0, aph = 0;
+      static_assert(TC_KT == 64, "tc_mma_ts_x4 issues the four K steps of a 64-k stage");
+      const uint32_t desc_hi = static_cast<uint32_t>(smem_desc_sw128(0) >> 32);
+      const uint32_t a_set = tmem + TC_COL_A + mset * 32;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
         int e, nt, row0, rows, ncols;
         decode(tile, e, nt, row0, rows, ncols);
         const uint32_t idesc = make_idesc(128, ncols);
         if (!mbar_wait(acc_empty_bar, (ti & 1u) ^ 1u, abort_flag, args.status)) break;
         tc_fence_after();
-        for (int st = 0; st < stages_per_tile; ++st, ++n) {
-          const int xs = n % TC_XSLOTS;
-          const int as = n % TC_ASLOTS;
+        for (int st = 0; st < stages_per_tile; ++st) {
           const uint32_t ab = 8u * (2 * as + mset);
-          if (!mbar_wait(xfull + 8u * xs, (n / TC_XSLOTS) & 1u, abort_flag, args.status) ||
-              !mbar_wait(a_ready + ab, (n / TC_ASLOTS) & 1u, abort_flag, args.status)) {
+          const uint32_t sub = static_cast<uint32_t>(st) & 1u;  // half of the token slot (tiles hold an even number of stages)
+          if ((sub == 0 && !mbar_wait(xfull + 8u * xs, xph, abort_flag, args.status)) ||
+              !mbar_wait(a_ready + ab, aph, abort_flag, args.status)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint64_t bdesc = smem_desc_sw128(x_base + xs * TC_XSLOT);
-#pragma unroll
-          for (int j = 0; j < TC_KT / 16; ++j) {
-            const uint32_t accum = (st > 0 || j > 0) ? 1u : 0u;
-            const uint64_t bd = bdesc + static_cast<uint64_t>((j * 32) >> 4);
-            tc_mma_ts(acc, tmem + TC_COL_A + as * 64 + mset * 32 + j * 8, bd, idesc, accum);
-          }
-          tc_commit(xempty + 8u * xs);
+          const uint32_t b_lo = ((x_base + xs * TC_XSLOT + sub * TC_XSUB) & 0x3FFFFu) >> 4;
+          tc_mma_ts_x4(acc, a_set + as * 64, b_lo, desc_hi, idesc, st > 0 ? 1u : 0u);
           tc_commit(a_free + ab);
+          if (sub) {
+            tc_commit(xempty + 8u * xs);
+            if (++xs == TC_XSLOTS) { xs = 0; xph ^= 1u; }
+          }
+          if (++as == TC_ASLOTS) { as = 0; aph ^= 1u; }
         }
         if (ok) tc_commit(acc_full_bar);
       }
