@@ -572,6 +572,10 @@ int launch_stream_gate_up(const void* xs, const int32_t* seg, int pairs, int max
   B200_REQUIRE(gate->rows % 64 == 0, "stream kernel: ffn (%d) must be a multiple of 64", gate->rows);
   if (pairs == 0) return B200MOE_OK;
   int S = pick_s(max_segment);
+  // max_segment is an upper bound (the token count); with several experts a
+  // segment of 33..64 rows is rare below 65 tokens and then takes two passes:
+  // 32-token chunks run on sixteen consumer warps and a smaller stage.
+  if (S == 8 && max_segment <= 64 && gate->experts >= 4) S = 4;
   // Tile height: 64 rows per set, or 112 where that fills the last wave of SMs
   // better (e.g. ffn 14336: 1792 items = 12.1 waves vs 1024 items = 6.9 waves).
   // The 112-row geometry has room for 16-token chunks only; longer segments are
@@ -628,7 +632,16 @@ int launch_stream_down(const void* a_in, const int32_t* seg, int pairs, int max_
   B200_REQUIRE(ksplit >= 1 && (down->cols / KT) % ksplit == 0, "stream kernel: bad k split %d",
                ksplit);
   if (pairs == 0) return B200MOE_OK;
-  const int S = pick_s(max_segment);
+  int S = pick_s(max_segment);
+  // max_segment is an upper bound (the token count): with top-k routing over
+  // several experts a segment of 17..32 rows is rare below 33 tokens, and then
+  // costs that expert a second pass; 16-token chunks keep the stage small (one
+  // more stage in the ring) for everybody else.
+  // The same one step up: 32-token chunks (sixteen consumer warps) for 33..64 tokens.
+  if (down->experts >= 4) {
+    if (S == 4) S = 2;
+    else if (S == 8 && max_segment <= 64) S = 4;
+  }
   CUtensorMap maps[8];
   if (int rc = weight_maps(down, &maps[0], &maps[2])) return rc;
   maps[1] = maps[0];
