@@ -573,9 +573,12 @@ int launch_stream_gate_up(const void* xs, const int32_t* seg, int pairs, int max
   if (pairs == 0) return B200MOE_OK;
   int S = pick_s(max_segment);
   // max_segment is an upper bound (the token count); with several experts a
-  // segment of 33..64 rows is rare below 65 tokens and then takes two passes:
-  // 32-token chunks run on sixteen consumer warps and a smaller stage.
-  if (S == 8 && max_segment <= 64 && gate->experts >= 4) S = 4;
+  // segment of more than half of it is rare and then takes two passes: chunks
+  // one size down mean a smaller stage (and sixteen consumer warps up to 64 tokens).
+  if (gate->experts >= 4) {
+    if (S == 4) S = 2;
+    else if (S == 8 && max_segment <= 64) S = 4;
+  }
   // Tile height: 64 rows per set, or 112 where that fills the last wave of SMs
   // better (e.g. ffn 14336: 1792 items = 12.1 waves vs 1024 items = 6.9 waves).
   // The 112-row geometry has room for 16-token chunks only; longer segments are
