@@ -587,11 +587,18 @@ int b200moe_ep_layer_forward(const b200moe_layer_t* L, const b200moe_ep_t* ep, c
     return rc;
   if (int rc = b200moe_ep_barrier(ep, epoch + 2, nullptr, stream)) return rc;
   prof_mark(pc, 3, st);
-  if (int rc = b200moe_gate_up(recv_x, w.seg2, cap_rows, max_segment, &L->gate, &L->up, L->activation,
+  // Chunk-size hint for the streaming kernel.  Its launchers take chunks one
+  // size below the caller's upper bound when they see four or more experts; a
+  // rank that holds fewer of a layer with at least four gets the same here (a
+  // segment longer than the chunk costs a second pass, nothing else).
+  int seg_hint = max_segment;
+  if (L->gate.experts < 4 && L->experts >= 4 && max_segment > 16 && max_segment <= 64)
+    seg_hint = (max_segment + 1) / 2;
+  if (int rc = b200moe_gate_up(recv_x, w.seg2, cap_rows, seg_hint, &L->gate, &L->up, L->activation,
                                regime, kp_mid, w.a, stream))
     return rc;
   prof_mark(pc, 4, st);
-  if (int rc = b200moe_down(w.a, w.seg2, cap_rows, max_segment, &L->down, regime, ksplit, w.dpart, stream))
+  if (int rc = b200moe_down(w.a, w.seg2, cap_rows, seg_hint, &L->down, regime, ksplit, w.dpart, stream))
     return rc;
   prof_mark(pc, 5, st);
   if (int rc = b200moe_ep_return(ep, w.dpart, ksplit, cap_rows, w.seg2, L->hidden, ret_rows, stream))
